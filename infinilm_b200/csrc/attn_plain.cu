@@ -7,6 +7,8 @@
 //
 // The query of token t is at absolute position p = tok_pos[t] of its request and sees cache
 // positions max(0, p - window + 1) .. p (window <= 0: all). Query head j reads kv head j / (nh / nkv).
+// With `dist_bias` (f32 [heads][dist_far + 1]) the scaled score of a key n positions back gets dist_bias[head][min(n, dist_far)]
+// added: a learned bias by distance that is constant from dist_far on.
 #include "common.cuh"
 
 // A lane holds head_dim / 32 elements of the query and of the output: 8 (head_dim <= 256) or 32 (<= 1024).
@@ -14,7 +16,8 @@ template <typename TA, int AP_MAX_PER_LANE>
 __global__ void attn_plain_kernel(const TA* __restrict__ qkv, int row_stride, TA* __restrict__ out,
                                   const TA* __restrict__ cache, const int* __restrict__ block_table, int bt_stride,
                                   const int* __restrict__ tok_pos, const int* __restrict__ tok_entry, int page_size,
-                                  int nh, int nkv, int hd, float scale, int window, const float* __restrict__ sink) {
+                                  int nh, int nkv, int hd, float scale, int window, const float* __restrict__ sink,
+                                  const float* __restrict__ dist_bias, int dist_far) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int j = blockIdx.y * (blockDim.x >> 5) + warp;
     const int t = blockIdx.x;
@@ -45,6 +48,7 @@ __global__ void attn_plain_kernel(const TA* __restrict__ qkv, int row_stride, TA
             if (d < hd) dot += q[r] * il_to_f(krow[d]);
         }
         dot = il_warp_sum(dot) * scale;
+        if (dist_bias) dot += dist_bias[(size_t)j * (dist_far + 1) + min(pos - kp, dist_far)];
         const float mn = fmaxf(m, dot);
         const float corr = expf(m - mn);  // exp(-inf) = 0 on the first key
         const float p = expf(dot - mn);
@@ -69,15 +73,16 @@ __global__ void attn_plain_kernel(const TA* __restrict__ qkv, int row_stride, TA
 IL_EXPORT int il_attn_plain(const void* qkv, int act_kind, int row_stride, void* out, const void* cache,
                             const int* block_table, int bt_stride, const int* tok_pos, const int* tok_entry,
                             int page_size, int T, int nh, int nkv, int hd, float scale, int window,
-                            const float* sink, cudaStream_t stream) {
+                            const float* sink, const float* dist_bias, int dist_far, cudaStream_t stream) {
     if (T <= 0) return IL_OK;
+    if (dist_bias && dist_far < 0) return IL_BAD_ARG;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || hd <= 0 || page_size <= 0) return IL_BAD_ARG;
     if (hd > 1024) return IL_UNSUPPORTED;
     const int warps = 4;
     dim3 grid(T, (nh + warps - 1) / warps);
 #define AP_LAUNCH(TA, N)                                                                                                                \
     attn_plain_kernel<TA, N><<<grid, warps * 32, 0, stream>>>((const TA*)qkv, row_stride, (TA*)out, (const TA*)cache, block_table, bt_stride, \
-                                                              tok_pos, tok_entry, page_size, nh, nkv, hd, scale, window, sink)
+                                                              tok_pos, tok_entry, page_size, nh, nkv, hd, scale, window, sink, dist_bias, dist_far)
     if (act_kind == IL_F32) {
         if (hd <= 256) AP_LAUNCH(float, 8); else AP_LAUNCH(float, 32);
     } else if (act_kind == IL_BF16) {

@@ -1,0 +1,116 @@
+// What stands between an attention mixer's projection and its attention when queries and keys are normed per head and
+// positions do not rotate anything: per token and head
+//   q_h <- q_h / sqrt(mean(q_h^2) + eps) * w_q * temp(pos)        temp(p) = 1 + coef * ln(floor((p + 1) / every) + 1)  (or 1)
+//   k_g <- k_g / sqrt(mean(k_g^2) + eps) * w_k                     -> the token's slot of the cache, K plane
+//   v_g                                                            -> the V plane: the value columns, or the key columns as
+//                                                                     projected, before the norm (a mixer whose values are its keys)
+// all in f32; w_q and w_k are one vector each, shared by the heads. Heads are laid out at hd >= key size, value size: the
+// surplus columns are written as zeros (a zero column adds nothing to a score). A mixer that reads another layer's cache
+// gives no key columns (k_off < 0): only its queries are normed.
+// Cache layout of one layer: [page][0=K,1=V][kv head][slot in page][hd]. One warp per (token, head).
+#include "common.cuh"
+
+template <typename TA>
+__global__ void qk_norm_store_kernel(const TA* proj, int ld, int q_off, int k_off, int v_off, int nh, int nkv, int dk, int dv, int hd,
+                                     const void* __restrict__ wq, const void* __restrict__ wk, int w_kind, float eps, float t_coef,
+                                     int t_every, TA* __restrict__ q_out, const int* __restrict__ tok_pos,
+                                     const int* __restrict__ tok_entry, const int* __restrict__ block_table, int bt_stride,
+                                     TA* __restrict__ cache, int page_size, int T) {
+    const int jobs = nh + (k_off >= 0 ? 2 * nkv : 0);
+    const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (wid >= (long long)T * jobs) return;
+    const int t = (int)(wid / jobs), j = (int)(wid - (long long)t * jobs);
+    const int pos = tok_pos[t];
+    il_pdl_wait();
+    const TA* row = proj + (size_t)t * ld;
+    if (j < nh) {                                 // a query head
+        const TA* x = row + q_off + (size_t)j * dk;
+        float ss = 0.f;
+        for (int d = lane; d < dk; d += 32) {
+            const float a = il_to_f(x[d]);
+            ss += a * a;
+        }
+        ss = il_warp_sum(ss);
+        float r = 1.f / sqrtf(ss / (float)dk + eps);
+        if (t_every > 0) r *= 1.f + t_coef * logf((float)((pos + 1) / t_every) + 1.f);
+        TA* o = q_out + ((size_t)t * nh + j) * hd;
+        for (int d = lane; d < hd; d += 32) o[d] = il_from_f<TA>(d < dk ? il_to_f(x[d]) * r * il_load_any(wq, w_kind, d) : 0.f);
+        return;
+    }
+    if (!cache) return;
+    const int page = block_table[(size_t)tok_entry[t] * bt_stride + pos / page_size];
+    if (page < 0) return;                         // the host reserves every page a step touches; never write elsewhere
+    const bool is_k = j < nh + nkv;
+    const int g = is_k ? j - nh : j - nh - nkv;
+    TA* dst = cache + (((size_t)page * 2 + (is_k ? 0 : 1)) * nkv + g) * (size_t)page_size * hd + (size_t)(pos % page_size) * hd;
+    if (is_k) {
+        const TA* x = row + k_off + (size_t)g * dk;
+        float ss = 0.f;
+        for (int d = lane; d < dk; d += 32) {
+            const float a = il_to_f(x[d]);
+            ss += a * a;
+        }
+        ss = il_warp_sum(ss);
+        const float r = 1.f / sqrtf(ss / (float)dk + eps);
+        for (int d = lane; d < hd; d += 32) dst[d] = il_from_f<TA>(d < dk ? il_to_f(x[d]) * r * il_load_any(wk, w_kind, d) : 0.f);
+    } else {
+        const TA* x = row + v_off + (size_t)g * dv;
+        for (int d = lane; d < hd; d += 32) dst[d] = d < dv ? x[d] : il_from_f<TA>(0.f);
+    }
+}
+
+IL_EXPORT int il_qk_norm_store(const void* proj, int act_kind, int ld, int q_off, int k_off, int v_off, int nh, int nkv, int dk, int dv, int hd,
+                               const void* wq, const void* wk, int w_kind, float eps, float t_coef, int t_every, void* q_out,
+                               const int* tok_pos, const int* tok_entry, const int* block_table, int bt_stride, void* cache, int page_size,
+                               int T, cudaStream_t stream) {
+    if (T <= 0) return IL_OK;
+    if (nh <= 0 || nkv <= 0 || dk <= 0 || dv <= 0 || hd < dk || hd < dv || page_size <= 0 || !wq || (k_off >= 0 && !wk)) return IL_BAD_ARG;
+    const long long warps = (long long)T * (nh + (k_off >= 0 ? 2 * nkv : 0));
+    const long long blocks = (warps + 3) / 4;
+    if (blocks > 0x7fffffffLL) return IL_UNSUPPORTED;
+    if (act_kind == IL_F32)
+        IL_LAUNCH(qk_norm_store_kernel<float>, (int)blocks, 128, 0, stream, (const float*)proj, ld, q_off, k_off, v_off, nh, nkv, dk, dv, hd, wq,
+                  wk, w_kind, eps, t_coef, t_every, (float*)q_out, tok_pos, tok_entry, block_table, bt_stride, (float*)cache, page_size, T);
+    else if (act_kind == IL_BF16)
+        IL_LAUNCH(qk_norm_store_kernel<__nv_bfloat16>, (int)blocks, 128, 0, stream, (const __nv_bfloat16*)proj, ld, q_off, k_off, v_off, nh, nkv,
+                  dk, dv, hd, wq, wk, w_kind, eps, t_coef, t_every, (__nv_bfloat16*)q_out, tok_pos, tok_entry, block_table, bt_stride,
+                  (__nv_bfloat16*)cache, page_size, T);
+    else
+        return IL_BAD_ARG;
+    IL_LAUNCH_CHECK();
+    return IL_OK;
+}
+
+// out[t, h * dv + c] = y[t, h * hd + c] * sigmoid(gate[t, g_off + h * dv + c]) for c < dv <= hd: a gate per output column,
+// and heads that were laid out at hd columns come out packed. Without a gate only the packing is done.
+template <typename TA>
+__global__ void gate_pack_kernel(const TA* y, int hd, const TA* gate, int ldg, int g_off, TA* __restrict__ out, int nh, int dv, int T) {
+    il_pdl_wait();
+    const int n = nh * dv;
+    const long long total = (long long)T * n;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / n;
+        const int jc = (int)(i - t * n), h = jc / dv, c = jc - h * dv;
+        float v = il_to_f(y[((size_t)t * nh + h) * hd + c]);
+        if (gate) v = v / (1.f + expf(-il_to_f(gate[(size_t)t * ldg + g_off + jc])));
+        out[i] = il_from_f<TA>(v);
+    }
+}
+
+IL_EXPORT int il_gate_pack(const void* y, int act_kind, int hd, const void* gate, int ldg, int g_off, void* out, int nh, int dv, int T,
+                           cudaStream_t stream) {
+    if (T <= 0) return IL_OK;
+    if (nh <= 0 || dv <= 0 || dv > hd) return IL_BAD_ARG;
+    const long long g = ((long long)T * nh * dv + 255) / 256;
+    const int blocks = (int)(g > 148 * 16 ? 148 * 16 : g);
+    if (act_kind == IL_F32)
+        IL_LAUNCH(gate_pack_kernel<float>, blocks, 256, 0, stream, (const float*)y, hd, (const float*)gate, ldg, g_off, (float*)out, nh, dv, T);
+    else if (act_kind == IL_BF16)
+        IL_LAUNCH(gate_pack_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)y, hd, (const __nv_bfloat16*)gate, ldg, g_off,
+                  (__nv_bfloat16*)out, nh, dv, T);
+    else
+        return IL_BAD_ARG;
+    IL_LAUNCH_CHECK();
+    return IL_OK;
+}

@@ -157,3 +157,86 @@ IL_EXPORT int il_add_rmsnorm(float* resid, const void* branch, float bscale, con
     IL_LAUNCH_CHECK();
     return IL_OK;
 }
+
+// ---- the norm on the branch, then the residual add -------------------------------------------------------------------
+//   resid[r] += scale * branch[r] / sqrt(mean(branch[r]^2) + eps) * w        (f32)
+//   copy[r]   = resid[r] in the activations' type (optional: what the next sublayer reads)
+// The block layout of a model whose sublayers read the residual stream itself and whose norms sit on the sublayers'
+// outputs. One block per row with a fixed thread count; the branch row waits in shared memory as f32 between the two passes.
+template <typename TA>
+__global__ void __launch_bounds__(256) norm_add_kernel(float* resid, const TA* branch, float scale, const void* __restrict__ w, int w_kind,
+                                                       float eps, TA* copy, int H) {
+    extern __shared__ float bs[];
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    il_pdl_wait();
+    const TA* br = branch + (size_t)r * H;
+    float* rr = resid + (size_t)r * H;
+    float ss = 0.f;
+    if ((H & 3) == 0) {
+        for (int v = threadIdx.x; v < (H >> 2); v += blockDim.x) {
+            const float4 b = ld4(br + 4 * v);
+            st4(bs + 4 * v, b);
+            ss += b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
+        }
+    } else {
+        for (int h = threadIdx.x; h < H; h += blockDim.x) {
+            const float b = il_to_f(br[h]);
+            bs[h] = b;
+            ss += b * b;
+        }
+    }
+    ss = il_block_sum(ss, red);
+    const float k = scale * (1.f / sqrtf(ss / (float)H + eps));
+    if ((H & 3) == 0) {
+        for (int v = threadIdx.x; v < (H >> 2); v += blockDim.x) {
+            const float4 b = ld4(bs + 4 * v);
+            const float4 wv = w_kind == IL_F32 ? ld4((const float*)w + 4 * v) : ld4((const __nv_bfloat16*)w + 4 * v);
+            float4 x = ld4(rr + 4 * v);
+            x.x = fmaf(k * b.x, wv.x, x.x), x.y = fmaf(k * b.y, wv.y, x.y), x.z = fmaf(k * b.z, wv.z, x.z), x.w = fmaf(k * b.w, wv.w, x.w);
+            st4(rr + 4 * v, x);
+            if (copy) st4(copy + (size_t)r * H + 4 * v, x);
+        }
+    } else {
+        for (int h = threadIdx.x; h < H; h += blockDim.x) {
+            const float x = fmaf(k * bs[h], il_load_any(w, w_kind, h), rr[h]);
+            rr[h] = x;
+            if (copy) copy[(size_t)r * H + h] = il_from_f<TA>(x);
+        }
+    }
+}
+
+// rows of f32 copied into the activations' type (the first sublayer's input, where no norm_add ran before it)
+template <typename TA>
+__global__ void cast_rows_kernel(const float* x, TA* out, size_t total) {
+    il_pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) out[i] = il_from_f<TA>(x[i]);
+}
+
+IL_EXPORT int il_norm_add(float* resid, const void* branch, float scale, const void* w, int w_kind, float eps, void* copy, int act_kind,
+                          int n_rows, int H, cudaStream_t stream) {
+    if (n_rows <= 0) return IL_OK;
+    if (H <= 0 || !branch) return IL_BAD_ARG;
+    const size_t smem = (size_t)H * sizeof(float);
+    if (smem > 200 * 1024) return IL_UNSUPPORTED;
+    if (act_kind == IL_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(norm_add_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        IL_LAUNCH(norm_add_kernel<float>, n_rows, 256, smem, stream, resid, (const float*)branch, scale, w, w_kind, eps, (float*)copy, H);
+    } else if (act_kind == IL_BF16) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(norm_add_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        IL_LAUNCH(norm_add_kernel<__nv_bfloat16>, n_rows, 256, smem, stream, resid, (const __nv_bfloat16*)branch, scale, w, w_kind, eps,
+                  (__nv_bfloat16*)copy, H);
+    } else
+        return IL_BAD_ARG;
+    IL_LAUNCH_CHECK();
+    return IL_OK;
+}
+
+IL_EXPORT int il_cast_rows(const float* x, void* out, int out_kind, long long total, cudaStream_t stream) {
+    if (total <= 0) return IL_OK;
+    if (out_kind != IL_BF16) return IL_BAD_ARG;
+    const long long g = (total + 255) / 256;
+    IL_LAUNCH(cast_rows_kernel<__nv_bfloat16>, (int)(g > 148 * 16 ? 148 * 16 : g), 256, 0, stream, x, (__nv_bfloat16*)out, (size_t)total);
+    IL_LAUNCH_CHECK();
+    return IL_OK;
+}

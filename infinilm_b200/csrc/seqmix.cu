@@ -253,6 +253,10 @@ IL_EXPORT int il_delta_prep(float* qk, int ld, int q_off, int k_off, int G, int 
 // thread, the column in shared memory (column c of row d at s[d * (ncol + 1) + c]: no bank is shared). Tokens in order:
 //   MODE 0 (decayed sum):  S = decay_h S + k v^T;                               o = S^T q
 //   MODE 1 (delta rule):   S = g_t S;  u = beta_t (v - S^T k);  S = S + k u^T;   o = S^T q
+//   MODE 3 (gated sum):    S = g_t S + beta_t k [v, 1]^T;                        o = S^T q   - per-token decay and input
+//                          weight; the state has one column more than v (vdim counts it), fed by the constant 1: it gathers
+//                          the weighted keys alone (the normaliser of a matrix memory), and the output's last column is its
+//                          product with q. v heads are vdim - 1 wide, the output's vdim.
 // q and k of SM_CHUNK tokens are staged in shared memory at a time. `in_act` 1: silu on q, k, v as they are read.
 // q/k head of value head h: h / (H / G). This form takes every size; key sizes up to 256 run the register form below
 // (`generic` 0), which gives the same sums in another order.
@@ -296,7 +300,8 @@ __global__ void matrix_state_scan_kernel(const float* __restrict__ q, const floa
         __syncthreads();
         for (int tt = 0; tt < nt; ++tt) {
             const size_t row = (size_t)(q0 + t0 + tt);
-            float vc = live ? v[row * ld_v + h * vdim + c] : 0.f;
+            float vc = MODE == 3 ? (c < vdim - 1 ? v[row * ld_v + h * (vdim - 1) + c] : c == vdim - 1 ? 1.f : 0.f)
+                                 : live ? v[row * ld_v + h * vdim + c] : 0.f;
             if (in_act) vc = sm_silu_fast(vc);
             const float* qq = qs + tt * dim;
             const float* kk = ks + tt * dim;
@@ -304,6 +309,13 @@ __global__ void matrix_state_scan_kernel(const float* __restrict__ q, const floa
             if (MODE == 0) {
                 for (int d = 0; d < dim; ++d) {
                     const float s = fmaf(dec, S[d * ncs + threadIdx.x], kk[d] * vc);
+                    S[d * ncs + threadIdx.x] = s;
+                    o = fmaf(s, qq[d], o);
+                }
+            } else if (MODE == 3) {
+                const float g = gdec[row * H + h], u = beta[row * H + h] * vc;
+                for (int d = 0; d < dim; ++d) {
+                    const float s = fmaf(g, S[d * ncs + threadIdx.x], kk[d] * u);
                     S[d * ncs + threadIdx.x] = s;
                     o = fmaf(s, qq[d], o);
                 }
@@ -389,7 +401,7 @@ __global__ void __launch_bounds__(SR_THREADS) matrix_state_scan_reg_kernel(
     const bool live = c < vdim;
     const int d0 = part * DPT;
     float S[DPT];
-    const float dec = MODE != 1 ? decay[h] : 0.f;
+    const float dec = (MODE == 0 || MODE == 2) ? decay[h] : 0.f;
     auto load_cols = [&](const float* src, float* dst) {      // this lane's DPT rows of column c from a [vdim][dim] matrix
         if (live && (dim & 3) == 0) {             // a column's rows lie together: 16 bytes a load (dim a multiple of 4 keeps them aligned)
 #pragma unroll
@@ -460,13 +472,20 @@ __global__ void __launch_bounds__(SR_THREADS) matrix_state_scan_reg_kernel(
             qr[j] = ok ? qp[j * TPT] : 0.f;
             kr[j] = (MODE != 2 && ok) ? kp[j * TPT] : 0.f;
         }
-        if (MODE != 2) {
+        if (MODE == 3) {                          // v heads are vdim - 1 wide; the state's last column is fed by the constant 1
+            const float* vp = v + row * ld_v + h * (vdim - 1) + blockIdx.z * cpb + s_l;
+#pragma unroll
+            for (int j = 0; j < NV; ++j) {
+                const int cc = blockIdx.z * cpb + s_l + j * TPT;
+                vr[j] = (tok && s_l + j * TPT < cpb) ? (cc < vdim - 1 ? vp[j * TPT] : cc == vdim - 1 ? 1.f : 0.f) : 0.f;
+            }
+        } else if (MODE != 2) {
             const float* vp = v + row * ld_v + h * vdim + blockIdx.z * cpb + s_l;
 #pragma unroll
             for (int j = 0; j < NV; ++j)
                 vr[j] = (tok && s_l + j * TPT < cpb && blockIdx.z * cpb + s_l + j * TPT < vdim) ? vp[j * TPT] : 0.f;
         }
-        if (MODE == 1 && tid < 2 * SR_CHUNK) {
+        if ((MODE == 1 || MODE == 3) && tid < 2 * SR_CHUNK) {
             const int tt = tid & (SR_CHUNK - 1);
             gr = t0 + tt < n ? (tid < SR_CHUNK ? gdec : beta)[(size_t)(q0 + t0 + tt) * H + h] : 0.f;
         }
@@ -483,7 +502,7 @@ __global__ void __launch_bounds__(SR_THREADS) matrix_state_scan_reg_kernel(
             for (int j = 0; j < NV; ++j)
                 if (s_l + j * TPT < cpb) vs[(s_tt << log_cpb) + s_l + j * TPT] = in_act ? sm_silu_fast(vr[j]) : vr[j];
         }
-        if (MODE == 1 && tid < 2 * SR_CHUNK) gb[tid] = gr;
+        if ((MODE == 1 || MODE == 3) && tid < 2 * SR_CHUNK) gb[tid] = gr;
     };
 
     fetch(0);
@@ -523,6 +542,18 @@ __global__ void __launch_bounds__(SR_THREADS) matrix_state_scan_reg_kernel(
                         S[4 * i + 1] = fmaf(dec, S[4 * i + 1], k4.y * vc);
                         S[4 * i + 2] = fmaf(dec, S[4 * i + 2], k4.z * vc);
                         S[4 * i + 3] = fmaf(dec, S[4 * i + 3], k4.w * vc);
+                        o0 = fmaf(S[4 * i], q4.x, o0), o1 = fmaf(S[4 * i + 1], q4.y, o1);
+                        o2 = fmaf(S[4 * i + 2], q4.z, o2), o3 = fmaf(S[4 * i + 3], q4.w, o3);
+                    }
+                } else if (MODE == 3) {
+                    const float g = gb[tt], u = gb[SR_CHUNK + tt] * vc;
+#pragma unroll
+                    for (int i = 0; i < DPT / 4; ++i) {
+                        const float4 k4 = kk[i], q4 = qq[i];
+                        S[4 * i] = fmaf(g, S[4 * i], k4.x * u);
+                        S[4 * i + 1] = fmaf(g, S[4 * i + 1], k4.y * u);
+                        S[4 * i + 2] = fmaf(g, S[4 * i + 2], k4.z * u);
+                        S[4 * i + 3] = fmaf(g, S[4 * i + 3], k4.w * u);
                         o0 = fmaf(S[4 * i], q4.x, o0), o1 = fmaf(S[4 * i + 1], q4.y, o1);
                         o2 = fmaf(S[4 * i + 2], q4.z, o2), o3 = fmaf(S[4 * i + 3], q4.w, o3);
                     }
@@ -624,7 +655,8 @@ IL_EXPORT int il_matrix_state_scan(int mode, const float* q, const float* k, con
     // seg_len > 0 (decayed sum, register form only): the entries' tokens in segments of seg_len, n_tiles of them at most
     // (a bound is enough), seg_state float32 [n_tiles, H, vdim, dim] scratch; two passes.
     if (seg_len > 0 && (mode != 0 || generic || single || dim > 256 || n_tiles <= 0 || !seg_state || seg_len % 8)) return IL_BAD_ARG;
-    if (H <= 0 || G <= 0 || H % G || dim <= 0 || vdim <= 0 || (mode != 0 && mode != 1)) return IL_BAD_ARG;
+    if (H <= 0 || G <= 0 || H % G || dim <= 0 || vdim <= 0 || (mode != 0 && mode != 1 && mode != 3)) return IL_BAD_ARG;
+    if (mode == 3 && (vdim < 2 || in_act)) return IL_BAD_ARG;
     if (mode == 0 ? !decay : (!beta || !gdec)) return IL_BAD_ARG;
     if (dim <= 256 && !generic) {
         // Rows of a column per lane (8 or 16) and lanes per column (a power of two up to 16) that cover dim. Few blocks (one
@@ -657,8 +689,10 @@ IL_EXPORT int il_matrix_state_scan(int mode, const float* q, const float* k, con
                 if (log_split <= 3) { if (dpt == 8) sr_launch<2, 8, 8, 8>(SR_ARGS); else sr_launch<2, 16, 8, 8>(SR_ARGS); }
                 else { if (dpt == 8) sr_launch<2, 8, 8, 16>(SR_ARGS); else sr_launch<2, 16, 8, 16>(SR_ARGS); }
             }
-        } else {
+        } else if (mode == 1) {
             if (dpt == 8) SR_PICK(1, 8); else SR_PICK(1, 16);
+        } else {
+            if (dpt == 8) SR_PICK(3, 8); else SR_PICK(3, 16);
         }
         IL_LAUNCH_CHECK();
         return IL_OK;
@@ -671,7 +705,11 @@ IL_EXPORT int il_matrix_state_scan(int mode, const float* q, const float* k, con
     }
     if (smem > 200 * 1024) return IL_UNSUPPORTED;
     const dim3 grid(E, H, (vdim + ncol - 1) / ncol);
-    if (mode == 0) {
+    if (mode == 3) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(matrix_state_scan_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        matrix_state_scan_kernel<3><<<grid, ncol, smem, stream>>>(q, k, v, ld_q, ld_k, ld_v, H, G, dim, vdim, in_act, decay, beta, gdec, state,
+                                                                  (size_t)slot_stride, read_slots, write_slots, qstart, out, ldo, e0);
+    } else if (mode == 0) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(matrix_state_scan_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         matrix_state_scan_kernel<0><<<grid, ncol, smem, stream>>>(q, k, v, ld_q, ld_k, ld_v, H, G, dim, vdim, in_act, decay, beta, gdec, state,
                                                                   (size_t)slot_stride, read_slots, write_slots, qstart, out, ldo, e0);
@@ -687,16 +725,22 @@ IL_EXPORT int il_matrix_state_scan(int mode, const float* q, const float* k, con
 // ---- a norm over groups of columns, times a gate -----------------------------------------------------------------------
 // out[t, j] = x[t, j] / sqrt(mean over j's group of x^2 + eps) * w[j % n_w] * act(gate[t, j]); groups of `group` columns;
 // act 0: sigmoid, 1: silu. x float32, the gate float32 or bfloat16, out float32 or bfloat16. One block per (row, group).
+// With `den_floor` (float32 [T, groups]) a group of x is group + 1 columns wide, its last column the read-out's normaliser:
+// the group is first divided by max(|x_scale * that column|, den_floor[t, g]) + den_eps (and multiplied by x_scale) - the
+// output of a matrix memory whose numerator and normaliser were read with the same unscaled query.
 template <typename TG, typename TO>
 __global__ void group_norm_gate_kernel(const float* __restrict__ x, int ldx, const void* __restrict__ w, int w_kind, int n_w, float eps,
-                                       const TG* __restrict__ gate, int ldg, int g_off, int act, TO* __restrict__ out, int ldo, int group) {
+                                       const TG* __restrict__ gate, int ldg, int g_off, int act, TO* __restrict__ out, int ldo, int group,
+                                       const float* __restrict__ den_floor, float x_scale, float den_eps) {
     __shared__ float red[32];
     const int t = blockIdx.x, j0 = blockIdx.y * group;
-    const float* xr = x + (size_t)t * ldx + j0;
+    const float* xr = x + (size_t)t * ldx + (den_floor ? blockIdx.y * (group + 1) : j0);
+    float pre = 1.f;
+    if (den_floor) pre = x_scale / (fmaxf(fabsf(x_scale * xr[group]), den_floor[(size_t)t * gridDim.y + blockIdx.y]) + den_eps);
     float ss = 0.f;
-    for (int j = threadIdx.x; j < group; j += blockDim.x) ss += xr[j] * xr[j];
+    for (int j = threadIdx.x; j < group; j += blockDim.x) ss += (xr[j] * pre) * (xr[j] * pre);
     ss = il_block_sum(ss, red);
-    const float r = 1.f / sqrtf(ss / (float)group + eps);
+    const float r = pre * (1.f / sqrtf(ss / (float)group + eps));
     for (int j = threadIdx.x; j < group; j += blockDim.x) {
         const float z = il_to_f(gate[(size_t)t * ldg + g_off + j0 + j]);
         const float a = act == 0 ? sm_sigmoid(z) : sm_silu(z);
@@ -704,9 +748,9 @@ __global__ void group_norm_gate_kernel(const float* __restrict__ x, int ldx, con
     }
 }
 
-IL_EXPORT int il_group_norm_gate(const float* x, int ldx, const void* w, int w_kind, int n_w, float eps, const void* gate, int gate_kind,
-                                 int ldg, int g_off, int act, void* out, int out_kind, int ldo, int group, int n_groups, int T,
-                                 cudaStream_t stream) {
+static int group_norm_gate_launch(const float* x, int ldx, const void* w, int w_kind, int n_w, float eps, const void* gate, int gate_kind,
+                                  int ldg, int g_off, int act, void* out, int out_kind, int ldo, int group, int n_groups, int T,
+                                  const float* den_floor, float x_scale, float den_eps, cudaStream_t stream) {
     if (T <= 0) return IL_OK;
     if (group <= 0 || n_groups <= 0 || n_w <= 0) return IL_BAD_ARG;
     // (a group of thousands of columns is one block: many threads, two to four columns each, keep its two passes short)
@@ -714,13 +758,93 @@ IL_EXPORT int il_group_norm_gate(const float* x, int ldx, const void* w, int w_k
     const dim3 grid(T, n_groups);
 #define GN_ARGS x, ldx, w, w_kind, n_w, eps
     if (gate_kind == IL_F32 && out_kind == IL_F32)
-        group_norm_gate_kernel<float, float><<<grid, threads, 0, stream>>>(GN_ARGS, (const float*)gate, ldg, g_off, act, (float*)out, ldo, group);
+        group_norm_gate_kernel<float, float><<<grid, threads, 0, stream>>>(GN_ARGS, (const float*)gate, ldg, g_off, act, (float*)out, ldo, group, den_floor, x_scale, den_eps);
     else if (gate_kind == IL_F32 && out_kind == IL_BF16)
-        group_norm_gate_kernel<float, __nv_bfloat16><<<grid, threads, 0, stream>>>(GN_ARGS, (const float*)gate, ldg, g_off, act, (__nv_bfloat16*)out, ldo, group);
+        group_norm_gate_kernel<float, __nv_bfloat16><<<grid, threads, 0, stream>>>(GN_ARGS, (const float*)gate, ldg, g_off, act, (__nv_bfloat16*)out, ldo, group, den_floor, x_scale, den_eps);
     else if (gate_kind == IL_BF16 && out_kind == IL_BF16)
-        group_norm_gate_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, threads, 0, stream>>>(GN_ARGS, (const __nv_bfloat16*)gate, ldg, g_off, act, (__nv_bfloat16*)out, ldo, group);
+        group_norm_gate_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, threads, 0, stream>>>(GN_ARGS, (const __nv_bfloat16*)gate, ldg, g_off, act, (__nv_bfloat16*)out, ldo, group, den_floor, x_scale, den_eps);
     else
         return IL_BAD_ARG;
+    IL_LAUNCH_CHECK();
+    return IL_OK;
+}
+
+IL_EXPORT int il_group_norm_gate(const float* x, int ldx, const void* w, int w_kind, int n_w, float eps, const void* gate, int gate_kind,
+                                 int ldg, int g_off, int act, void* out, int out_kind, int ldo, int group, int n_groups, int T,
+                                 cudaStream_t stream) {
+    return group_norm_gate_launch(x, ldx, w, w_kind, n_w, eps, gate, gate_kind, ldg, g_off, act, out, out_kind, ldo, group, n_groups, T,
+                                  nullptr, 1.f, 0.f, stream);
+}
+
+// x [T, groups * (group + 1)]: every group followed by its normaliser column (see the kernel).
+IL_EXPORT int il_group_norm_gate_den(const float* x, int ldx, const void* w, int w_kind, int n_w, float eps, const void* gate, int gate_kind,
+                                     int ldg, int g_off, int act, void* out, int out_kind, int ldo, int group, int n_groups, int T,
+                                     const float* den_floor, float x_scale, float den_eps, cudaStream_t stream) {
+    if (!den_floor) return IL_BAD_ARG;
+    return group_norm_gate_launch(x, ldx, w, w_kind, n_w, eps, gate, gate_kind, ldg, g_off, act, out, out_kind, ldo, group, n_groups, T,
+                                  den_floor, x_scale, den_eps, stream);
+}
+
+// ---- log-space gates with a running maximum ------------------------------------------------------------------------------
+// A matrix memory with exponential gates keeps its sums scaled by exp(-m), m the running maximum of the log weights:
+//   i_t = cap tanh(zi_t / cap),  f_t = logsigmoid(cap tanh(zf_t / cap))          (cap <= 0: zi, logsigmoid(zf) as they are)
+//   m_t = max(f_t + m_(t-1), i_t);  decay_t = exp(f_t + m_(t-1) - m_t);  inw_t = exp(i_t - m_t);  floor_t = exp(-m_t)
+// m is part of the request's state (float32 [slots, heads]; the zero slot gives m = 0). zi, zf: float32 columns of z, one per
+// head. One block per (entry, head): the transcendental parts are done by all threads for 128 tokens at a time, the chain
+// of maxima by one thread in the order of the sequence (an add and a max a token), so a token's gates do not depend on
+// how the sequence was cut into steps.
+#define SG_TOK 128
+__device__ __forceinline__ float sm_logsigmoid(float x) { return x >= 0.f ? -log1pf(expf(-x)) : x - log1pf(expf(x)); }
+__global__ void __launch_bounds__(SG_TOK) stabilized_gates_kernel(const float* z, int ldz, int i_off, int f_off, float cap, float* mstate,
+                                                                  int slot_stride, const int* __restrict__ read_slots,
+                                                                  const int* __restrict__ write_slots, const int* __restrict__ qstart,
+                                                                  float* __restrict__ decay, float* __restrict__ inw,
+                                                                  float* __restrict__ floor_, int H, int e0) {
+    __shared__ float si[SG_TOK], sf[SG_TOK], sm_[SG_TOK + 1];
+    const int e = e0 + blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int q0 = qstart[e], n = qstart[e + 1] - q0;
+    if (n <= 0) return;
+    if (tid == 0) sm_[0] = mstate[(size_t)read_slots[e] * slot_stride + h];
+    for (int t0 = 0; t0 < n; t0 += SG_TOK) {
+        const int nt = min(SG_TOK, n - t0);
+        float il = 0.f, fl = 0.f;
+        if (tid < nt) {
+            const size_t row = (size_t)(q0 + t0 + tid);
+            const float zi = z[row * ldz + i_off + h], zf = z[row * ldz + f_off + h];
+            il = cap > 0.f ? cap * tanhf(zi / cap) : zi;
+            fl = sm_logsigmoid(cap > 0.f ? cap * tanhf(zf / cap) : zf);
+            si[tid] = il, sf[tid] = fl;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            float m = sm_[0];
+            for (int i = 0; i < nt; ++i) {
+                m = fmaxf(sf[i] + m, si[i]);
+                sm_[i + 1] = m;
+            }
+        }
+        __syncthreads();
+        if (tid < nt) {
+            const size_t o = (size_t)(q0 + t0 + tid) * H + h;
+            const float mp = sm_[tid], m = sm_[tid + 1];
+            decay[o] = expf(fl + mp - m);
+            inw[o] = expf(il - m);
+            floor_[o] = expf(-m);
+        }
+        __syncthreads();
+        if (tid == 0) sm_[0] = sm_[nt];
+    }
+    __syncthreads();
+    if (tid == 0) mstate[(size_t)write_slots[e] * slot_stride + h] = sm_[0];
+}
+
+IL_EXPORT int il_stabilized_gates(const float* z, int ldz, int i_off, int f_off, float cap, float* mstate, int slot_stride, const int* read_slots,
+                                  const int* write_slots, const int* qstart, float* decay, float* inw, float* floor_, int H, int E, int e0,
+                                  cudaStream_t stream) {
+    if (E <= 0) return IL_OK;
+    if (H <= 0 || e0 < 0 || slot_stride < H) return IL_BAD_ARG;
+    stabilized_gates_kernel<<<dim3(E, H), SG_TOK, 0, stream>>>(z, ldz, i_off, f_off, cap, mstate, slot_stride, read_slots, write_slots, qstart,
+                                                                decay, inw, floor_, H, e0);
     IL_LAUNCH_CHECK();
     return IL_OK;
 }

@@ -5,7 +5,7 @@ import importlib
 
 from .causal_lm import CausalLM
 
-BUILTIN = ("minicpm4", "nirozen", "gopitar")
+BUILTIN = ("minicpm4", "nirozen", "gopitar", "somipel")
 
 
 def register_builtin() -> None:

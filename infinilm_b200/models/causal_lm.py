@@ -11,6 +11,7 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
+from .. import ops
 from ..parts.base import Part, build_part, part_class
 from ..parts.spec import CacheNeed, ModelSpec, WeightSpec
 
@@ -113,6 +114,8 @@ class CausalLM:
         logits = ctx.ws.rows("logits", n, self.vocab, torch.float32)
         if n == 0:
             return logits
+        if isinstance(pending, ops.ResidualCopy):         # the last block added its branches itself
+            pending = None
         branch, bscale = pending if pending is not None else (None, 1.0)
         normed = self.final_norm.add_norm(resid, branch, bscale, ctx.ws.rows("final_normed", n, self.hidden, self.dtype),
                                           rows=ctx.want_rows)

@@ -203,12 +203,14 @@ def rope_store(qkv: torch.Tensor, tok_pos: torch.Tensor, tok_entry: torch.Tensor
 def attention_plain(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                     tok_pos: torch.Tensor, tok_entry: torch.Tensor, page_size: int, n_heads: int,
                     n_kv_heads: int, head_dim: int, scale: float, window: Optional[int] = None,
-                    sink: Optional[torch.Tensor] = None) -> None:
+                    sink: Optional[torch.Tensor] = None, dist_bias: Optional[torch.Tensor] = None) -> None:
     """Causal attention of every token of `qkv` over its request's cache pages (plain kernel). `qkv` needs the query
     heads only (keys and values are read from the cache). `sink`: float32 [heads], a score per head that joins the
-    softmax's denominator without a value."""
-    _need_cuda(qkv, out, cache, block_table, tok_pos, tok_entry, sink)
+    softmax's denominator without a value. `dist_bias`: float32 [heads, far + 1], added to the scaled score of a key n
+    positions back as dist_bias[head, min(n, far)]."""
+    _need_cuda(qkv, out, cache, block_table, tok_pos, tok_entry, sink, dist_bias)
     _check_sink(sink, n_heads)
+    _check_dist_bias(dist_bias, n_heads)
     T = qkv.shape[0]
     if out.shape != (T, n_heads * head_dim) or out.dtype != qkv.dtype or cache.dtype != qkv.dtype:
         raise KernelError("attention_plain: out [T, heads*head_dim], same dtype as qkv and cache")
@@ -217,15 +219,98 @@ def attention_plain(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, b
     _contig("qkv", qkv), _contig("out", out), _contig("cache", cache), _contig("block_table", block_table)
     f = _fn("attn_plain", "il_attn_plain", [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int,
                                             _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
-                                            _c_int, _c_void_p, _c_void_p])
+                                            _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p])
     _check(f(_ptr(qkv), kind_of(qkv.dtype), qkv.shape[1], _ptr(out), _ptr(cache), _ptr(block_table),
              block_table.shape[1], _ptr(tok_pos), _ptr(tok_entry), page_size, T, n_heads, n_kv_heads, head_dim,
-             scale, int(window or 0), _ptr(sink), _stream()), "attention_plain")
+             scale, int(window or 0), _ptr(sink), _ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[1] - 1, _stream()),
+           "attention_plain")
 
 
 def _check_sink(sink: Optional[torch.Tensor], n_heads: int) -> None:
     if sink is not None and (sink.dtype != torch.float32 or sink.numel() != n_heads or not sink.is_contiguous()):
         raise KernelError("attention: sink must be a contiguous float32 tensor, one number per query head")
+
+
+def _check_dist_bias(dist_bias: Optional[torch.Tensor], n_heads: int) -> None:
+    if dist_bias is not None and (dist_bias.dtype != torch.float32 or dist_bias.dim() != 2 or dist_bias.shape[0] != n_heads
+                                  or dist_bias.shape[1] < 1 or not dist_bias.is_contiguous()):
+        raise KernelError("attention: the distance bias must be a contiguous float32 [heads, far + 1] tensor")
+
+
+def norm_add(resid: torch.Tensor, branch: torch.Tensor, weight: torch.Tensor, eps: float, scale: float,
+             copy: Optional[torch.Tensor] = None) -> None:
+    """resid += scale * branch / sqrt(mean(branch^2) + eps) * weight, row by row in float32 (resid float32 [T,H], in place);
+    `copy` (of branch's dtype, [T,H]) receives the new rows of resid: what the next sublayer of a model reads whose norms sit
+    on the sublayers' outputs."""
+    _need_cuda(resid, branch, weight, copy)
+    T, H = resid.shape
+    if resid.dtype != torch.float32 or tuple(branch.shape) != (T, H) or weight.numel() != H:
+        raise KernelError("norm_add: resid float32 [T,H], branch [T,H], weight [H]")
+    if copy is not None and (tuple(copy.shape) != (T, H) or copy.dtype != branch.dtype or not copy.is_contiguous()):
+        raise KernelError("norm_add: copy [T,H] of the branch's dtype")
+    _contig("resid", resid), _contig("branch", branch), _contig("weight", weight)
+    f = _fn("rmsnorm", "il_norm_add", [_c_void_p, _c_void_p, _c_float, _c_void_p, _c_int, _c_float, _c_void_p, _c_int, _c_int, _c_int,
+                                       _c_void_p])
+    _check(f(_ptr(resid), _ptr(branch), scale, _ptr(weight), kind_of(weight.dtype), eps, _ptr(copy), kind_of(branch.dtype), T, H,
+             _stream()), "norm_add")
+
+
+def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x rounded to bfloat16; x contiguous float32, out of the same shape."""
+    _need_cuda(x, out)
+    if x.dtype != torch.float32 or out.dtype != torch.bfloat16 or x.shape != out.shape:
+        raise KernelError("cast_rows: float32 in, bfloat16 out, one shape")
+    _contig("x", x), _contig("out", out)
+    f = _fn("rmsnorm", "il_cast_rows", [_c_void_p, _c_void_p, _c_int, _c_ll, _c_void_p])
+    _check(f(_ptr(x), _ptr(out), BF16, x.numel(), _stream()), "cast_rows")
+
+
+def qk_norm_store(proj: torch.Tensor, q_off: int, k_off: Optional[int], v_off: int, n_heads: int, n_kv_heads: int, qk_dim: int, v_dim: int,
+                  head_dim: int, w_q: torch.Tensor, w_k: Optional[torch.Tensor], eps: float, temp_coef: float, temp_every: int,
+                  q_out: torch.Tensor, tok_pos: torch.Tensor, tok_entry: torch.Tensor, block_table: torch.Tensor,
+                  cache: Optional[torch.Tensor], page_size: int) -> None:
+    """Per token and head: q / rms(q) * w_q (times 1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1) if temp_every > 0)
+    to `q_out` [T, heads * head_dim]; k / rms(k) * w_k to the K plane of the token's cache slot and the value columns (at
+    `v_off`; the key columns themselves where the values are the keys as projected) to the V plane. Heads are laid out at
+    head_dim >= qk_dim, v_dim, the surplus zero. `k_off` None: the mixer has no keys of its own, only queries are normed."""
+    _need_cuda(proj, w_q, w_k, q_out, tok_pos, tok_entry, block_table, cache)
+    T = proj.shape[0]
+    has_k = k_off is not None
+    if proj.stride(1) != 1 or q_off + n_heads * qk_dim > proj.shape[1] or (has_k and (k_off + n_kv_heads * qk_dim > proj.shape[1]
+                                                                                    or v_off + n_kv_heads * v_dim > proj.shape[1])):
+        raise KernelError("qk_norm_store: segments lie outside the rows")
+    if w_q.numel() != qk_dim or (has_k and (w_k is None or w_k.numel() != qk_dim or w_k.dtype != w_q.dtype)):
+        raise KernelError("qk_norm_store: one norm weight of qk_dim entries for the queries and one for the keys, of one dtype")
+    if tuple(q_out.shape) != (T, n_heads * head_dim) or q_out.dtype != proj.dtype or not q_out.is_contiguous():
+        raise KernelError("qk_norm_store: q_out [T, heads * head_dim] of proj's dtype")
+    _i32("qk_norm_store", tok_pos, tok_entry, block_table)
+    _contig("block_table", block_table)
+    if cache is not None:
+        _contig("cache", cache)
+        if cache.dtype != proj.dtype or tuple(cache.shape[1:]) != (2, n_kv_heads, page_size, head_dim):
+            raise KernelError("qk_norm_store: cache [pages,2,kv_heads,page,head_dim] of proj's dtype")
+    f = _fn("qk_norm", "il_qk_norm_store", [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                            _c_void_p, _c_void_p, _c_int, _c_float, _c_float, _c_int, _c_void_p, _c_void_p, _c_void_p,
+                                            _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p])
+    _check(f(_ptr(proj), kind_of(proj.dtype), proj.stride(0), q_off, k_off if has_k else -1, v_off, n_heads, n_kv_heads, qk_dim, v_dim,
+             head_dim, _ptr(w_q), _ptr(w_k), kind_of(w_q.dtype), eps, temp_coef, temp_every, _ptr(q_out), _ptr(tok_pos), _ptr(tok_entry),
+             _ptr(block_table), block_table.shape[1], _ptr(cache if has_k else None), page_size, T, _stream()), "qk_norm_store")
+
+
+def gate_pack(y: torch.Tensor, head_dim: int, gate: Optional[torch.Tensor], g_off: int, out: torch.Tensor, n_heads: int, v_dim: int) -> None:
+    """out[t, h*v_dim + c] = y[t, h*head_dim + c] * sigmoid(gate[t, g_off + h*v_dim + c]) for c < v_dim: a gate per output
+    column, and heads laid out at head_dim columns come out packed (`gate` None: only that)."""
+    _need_cuda(y, gate, out)
+    T = y.shape[0]
+    if y.dtype != out.dtype or not y.is_contiguous() or not out.is_contiguous():
+        raise KernelError("gate_pack: one dtype, contiguous tensors")
+    if gate is not None and (gate.dtype != y.dtype or gate.stride(1) != 1 or g_off + n_heads * v_dim > gate.shape[1]):
+        raise KernelError("gate_pack: the gate has y's dtype and one column per output column")
+    if y.shape[1] != n_heads * head_dim or tuple(out.shape) != (T, n_heads * v_dim):
+        raise KernelError("gate_pack: shapes")
+    f = _fn("qk_norm", "il_gate_pack", [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(_ptr(y), kind_of(y.dtype), head_dim, _ptr(gate), 0 if gate is None else gate.stride(0), g_off, _ptr(out), n_heads, v_dim, T,
+             _stream()), "gate_pack")
 
 
 def gemm_f32(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, alpha: float = 1.0,
@@ -429,6 +514,15 @@ def attention_prefill_tc5(qkv: torch.Tensor, out: torch.Tensor, kv_map: torch.Te
 
 
 SKINNY_MAX_ROWS = 16
+
+
+class ResidualCopy:
+    """What a block hands to the next when nothing is pending: the residual stream is complete, and `rows` holds it in the
+    compute dtype (the float32 stream itself on the 32-bit path) for a sublayer that reads the stream as it is."""
+    __slots__ = ("rows",)
+
+    def __init__(self, rows: torch.Tensor):
+        self.rows = rows
 
 
 class NormedInput:
@@ -1038,7 +1132,7 @@ def delta_prep(qk: torch.Tensor, q_off: int, k_off: int, n_qk_heads: int, dim: i
              _ptr(a_log), _ptr(dt_bias), _ptr(beta), _ptr(gdec), n_heads, T, _stream()), "delta_prep")
 
 
-SCAN_DECAY, SCAN_DELTA = 0, 1
+SCAN_DECAY, SCAN_DELTA, SCAN_GATED = 0, 1, 3
 
 
 def matrix_state_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, n_heads: int, n_qk_heads: int, dim: int,
@@ -1048,6 +1142,8 @@ def matrix_state_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tens
                       single: bool = False, seg_len: int = 0, n_tiles: int = 0, seg_state: Optional[torch.Tensor] = None) -> None:
     """A recurrence over a float32 state S [dim, vdim] per (request, head), token by token in each entry's order.
     SCAN_DECAY: S = decay[h] S + k v^T, o = S^T q. SCAN_DELTA: S = g S; u = beta (v - S^T k); S += k u^T; o = S^T q.
+    SCAN_GATED: S = g S + beta k [v, 1]^T, o = S^T q with g, beta per token and head (`gdec`, `beta`); the state and the output
+    have one column more than v (`vdim` counts it: v heads are vdim - 1 wide), fed by the constant 1.
     q, k float32 [T, >= n_qk_heads*dim] (views with a row stride), v float32 [T, >= n_heads*vdim], out float32 [T, n_heads*vdim];
     value head h reads q/k head h // (n_heads // n_qk_heads). in_act 1: silu on q, k, v as read.
     state float32 [slots, n_heads, vdim, dim] (S column by column: the dim entries behind one output lie together). `generic`: the kernel that keeps the state in shared memory (any size; the
@@ -1063,7 +1159,8 @@ def matrix_state_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tens
             raise KernelError("matrix_state_scan: float32 tensors with contiguous rows")
     if not state.is_contiguous() or tuple(state.shape[1:]) != (n_heads, vdim, dim):
         raise KernelError("matrix_state_scan: state float32 [slots, heads, vdim, dim]")
-    if out.shape[1] != n_heads * vdim or q.shape[1] < n_qk_heads * dim or k.shape[1] < n_qk_heads * dim or v.shape[1] < n_heads * vdim:
+    v_cols = n_heads * (vdim - 1 if mode == SCAN_GATED else vdim)
+    if out.shape[1] != n_heads * vdim or q.shape[1] < n_qk_heads * dim or k.shape[1] < n_qk_heads * dim or v.shape[1] < v_cols:
         raise KernelError("matrix_state_scan: shapes")
     if seg_len > 0:
         _need_cuda(seg_state)
@@ -1112,15 +1209,58 @@ def silu_cols(x: torch.Tensor, cols: int) -> None:
     _check(f(_ptr(x), x.stride(0), cols, x.shape[0], _stream()), "silu_cols")
 
 
+def stabilized_gates(z: torch.Tensor, i_off: int, f_off: int, cap: float, m_state: torch.Tensor, read_slots: torch.Tensor,
+                     write_slots: torch.Tensor, entry_qstart: torch.Tensor, n_entries: int, decay: torch.Tensor, in_weight: torch.Tensor,
+                     den_floor: torch.Tensor, n_heads: int, first_entry: int = 0) -> None:
+    """Log-space gates of a matrix memory with their running maximum m (part of the request's state, float32 [slots, heads]):
+    i = cap tanh(z[:, i_off + h] / cap), f = logsigmoid(cap tanh(z[:, f_off + h] / cap)) (cap <= 0: no cap);
+    m_t = max(f_t + m_(t-1), i_t); decay = exp(f + m_(t-1) - m_t), in_weight = exp(i - m_t), den_floor = exp(-m_t): float32 [T, heads]."""
+    _need_cuda(z, m_state, read_slots, write_slots, entry_qstart, decay, in_weight, den_floor)
+    _i32("stabilized_gates", read_slots, write_slots, entry_qstart)
+    T = z.shape[0]
+    if z.dtype != torch.float32 or z.stride(1) != 1 or max(i_off, f_off) + n_heads > z.shape[1]:
+        raise KernelError("stabilized_gates: z float32 with a column per head at both offsets")
+    if m_state.dtype != torch.float32 or not m_state.is_contiguous() or m_state.dim() != 2 or m_state.shape[1] != n_heads:
+        raise KernelError("stabilized_gates: m_state float32 [slots, heads]")
+    for t in (decay, in_weight, den_floor):
+        if t.dtype != torch.float32 or tuple(t.shape) != (T, n_heads) or not t.is_contiguous():
+            raise KernelError("stabilized_gates: outputs float32 [T, heads]")
+    f = _fn("seqmix", "il_stabilized_gates", [_c_void_p, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
+                                              _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(_ptr(z), z.stride(0), i_off, f_off, cap, _ptr(m_state), m_state.stride(0), _ptr(read_slots), _ptr(write_slots),
+             _ptr(entry_qstart), _ptr(decay), _ptr(in_weight), _ptr(den_floor), n_heads, n_entries, first_entry, _stream()),
+           "stabilized_gates")
+
+
 GATE_SIGMOID, GATE_SILU = 0, 1
 
 
 def group_norm_gate(x: torch.Tensor, w: torch.Tensor, eps: float, gate: torch.Tensor, g_off: int, act: int, out: torch.Tensor,
-                    group: int) -> None:
+                    group: int, den_floor: Optional[torch.Tensor] = None, x_scale: float = 1.0, den_eps: float = 0.0) -> None:
     """out[t,j] = x[t,j] / sqrt(mean of x^2 over j's group of `group` columns + eps) * w[j % len(w)] * act(gate[t, g_off+j]);
-    x float32 [T,n], gate float32 or bfloat16 (a view with a row stride), out float32 or bfloat16 [T,n]."""
-    _need_cuda(x, w, gate, out)
-    T, n = x.shape
+    x float32 [T,n], gate float32 or bfloat16 (a view with a row stride), out float32 or bfloat16 [T,n].
+    With `den_floor` (float32 [T, groups]) x is [T, groups * (group + 1)], every group followed by its normaliser column c:
+    the group is first multiplied by x_scale and divided by max(|x_scale * c|, den_floor[t, g]) + den_eps."""
+    _need_cuda(x, w, gate, out, den_floor)
+    T = x.shape[0]
+    if den_floor is not None:
+        n_groups = x.shape[1] // (group + 1)
+        if (x.shape[1] != n_groups * (group + 1) or den_floor.dtype != torch.float32 or tuple(den_floor.shape) != (T, n_groups)
+                or not den_floor.is_contiguous()):
+            raise KernelError("group_norm_gate: with a denominator x is [T, groups * (group + 1)] and den_floor float32 [T, groups]")
+        n = n_groups * group
+        if x.dtype != torch.float32 or x.stride(1) != 1 or out.stride(1) != 1 or gate.stride(1) != 1 or tuple(out.shape) != (T, n):
+            raise KernelError("group_norm_gate: x float32, out [T, groups * group]")
+        if g_off + n > gate.shape[1] or not w.is_contiguous():
+            raise KernelError("group_norm_gate: the gate must cover the row")
+        f = _fn("seqmix", "il_group_norm_gate_den", [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_float, _c_void_p, _c_int, _c_int,
+                                                     _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_float,
+                                                     _c_float, _c_void_p])
+        _check(f(_ptr(x), x.stride(0), _ptr(w), kind_of(w.dtype), w.numel(), eps, _ptr(gate), kind_of(gate.dtype), gate.stride(0), g_off,
+                 act, _ptr(out), kind_of(out.dtype), out.stride(0), group, n_groups, T, _ptr(den_floor), x_scale, den_eps, _stream()),
+               "group_norm_gate")
+        return
+    n = x.shape[1]
     if x.dtype != torch.float32 or x.stride(1) != 1 or out.stride(1) != 1 or gate.stride(1) != 1 or tuple(out.shape) != (T, n):
         raise KernelError("group_norm_gate: x float32 [T,n], out [T,n]")
     if n % group or g_off + n > gate.shape[1] or not w.is_contiguous():

@@ -26,7 +26,9 @@ class PagedAttend:
     attention mixer of any kind calls once its queries stand in rows and its keys and values in the cache.
     `sink`: float32 [heads] on the device or None - a score per head that joins the softmax's denominator without a value.
     `shared_kv`: the mixer writes the same vector to the K and the V plane (one latent that is key and value); the decode
-    kernel then reads the K plane alone. The prompt kernels, bound by arithmetic, read both planes as they lie."""
+    kernel then reads the K plane alone. The prompt kernels, bound by arithmetic, read both planes as they lie.
+    `dist_bias`: float32 [heads, far + 1] on the device or None - a bias by distance, added to the scaled score of a key n
+    positions back as dist_bias[head, min(n, far)] (constant from `far` on)."""
 
     # The fast bfloat16 kernels take kernel pages of 16 keys (the cache manager lays larger pages out as runs of them)
     # and at most 64 query heads per kv head; anything else, and the whole float32 path, runs the plain kernel.
@@ -41,10 +43,11 @@ class PagedAttend:
         self.dtype, self.nh, self.nkv, self.hd, self.scale, self.window = dtype, n_heads, n_kv_heads, head_dim, scale, window
         self.force_plain, self.prefill_kernel, self.shared_kv = force_plain, prefill_kernel, shared_kv
         self.sink: Optional[torch.Tensor] = None
+        self.dist_bias: Optional[torch.Tensor] = None
 
     def fast_ok(self, page_size: int) -> bool:
         return (self.dtype == torch.bfloat16 and page_size == self.FAST_PAGE and self.nh // self.nkv <= self.FAST_MAX_GROUP
-                and not self.force_plain and self.hd % 16 == 0 and 16 <= self.hd <= 256)
+                and not self.force_plain and self.hd % 16 == 0 and 16 <= self.hd <= 256 and self.dist_bias is None)
 
     def decode_splits(self, base: int, max_pages: int, resident: int) -> int:
         """Splits of the keys for `base` blocks per split: as many as fill the wanted share of one wave of blocks
@@ -63,7 +66,7 @@ class PagedAttend:
                               "head sizes in steps of 16 up to 256): the plain kernel runs, at a fraction of their speed",
                               RuntimeWarning, stacklevel=2)
             ops.attention_plain(qkv, out, cache.storage, cache.block_table, ctx.tok_pos, ctx.tok_entry,
-                                cache.page_size, self.nh, self.nkv, self.hd, self.scale, self.window, self.sink)
+                                cache.page_size, self.nh, self.nkv, self.hd, self.scale, self.window, self.sink, self.dist_bias)
             return
         n_dec, E = ctx.n_decode, ctx.n_entries
         if n_dec > 0:

@@ -181,5 +181,5 @@ def _ensure_builtin() -> None:
     global _builtin_done
     if not _builtin_done:
         _builtin_done = True
-        from . import (attention, blocks, conv_attention, embedding, feed_forward, latent_attention, linear_recurrence, moe, norms,  # noqa: F401
-                       parallel, position)
+        from . import (attention, blocks, conv_attention, embedding, feed_forward, latent_attention, linear_recurrence, moe, normed_attention,  # noqa: F401
+                       norms, parallel, position)

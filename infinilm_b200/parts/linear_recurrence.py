@@ -9,6 +9,11 @@ GatedDeltaRule:
     beta = sigmoid(W_b h),  g = exp(-exp(A_log) softplus(W_a h + dt_bias))
     per head  S = g S;  u = beta (v - S^T k);  S = S + k u^T;  o = S^T q      (the read-out sees the token's own write)
     y = W_o ( rms_norm(o per head) * w * silu(W_g h) )
+MatrixLSTM (the matrix memory of an xLSTM block, with exponential gates kept in log space under a running maximum m):
+    q = W_q h / sqrt(dim), k = W_k h, v = W_v h;  i = cap tanh((W_i h + b_i) / cap),  f = logsigmoid(cap tanh((W_f h + b_f) / cap))
+    m_t = max(f + m_(t-1), i);  S_t = exp(f + m_(t-1) - m_t) S_(t-1) + exp(i - m_t) k v^T;  n_t the same with k alone
+    o = S_t^T q / (max(|n_t . q|, exp(-m_t)) + 1e-6);  y = W_o ( rms_norm(o per head) * w * sigmoid(W_g h) )
+    (S, n and m start at zero; the state is S with n as one more column, and m)
 The projections leave float32 on both paths (what enters a recurrence, its gates and decays stay 32-bit).
 """
 from __future__ import annotations
@@ -168,5 +173,71 @@ class GatedDeltaRule(_FusableEnds, Mixer):
         return self._output(gated, ctx, tail, "gdr_branch")
 
 
+class MatrixLSTM(Mixer):
+    """params: hidden, n_heads, qk_dim, v_dim, gate_cap (None or 0: the gates' pre-activations are not capped), eps (of the
+    output norm), den_eps (added to the read-out's denominator, default 1e-6).
+    Tensors: q, k [heads * qk_dim, in], v, g [heads * v_dim, in], i, f [heads, in], i.b, f.b [heads], o, norm [heads * v_dim]."""
+    graph_safe = True
+
+    def __init__(self, params, prefix, dtype):
+        super().__init__(params, prefix, dtype)
+        p = params
+        self.hidden, self.nh, self.dk, self.dv = int(p["hidden"]), int(p["n_heads"]), int(p["qk_dim"]), int(p["v_dim"])
+        if min(self.hidden, self.nh, self.dk, self.dv) <= 0:
+            raise ValueError("matrix memory: sizes must be positive")
+        self.cap = float(p.get("gate_cap") or 0.0)
+        self.eps, self.den_eps = float(p["eps"]), float(p.get("den_eps", 1e-6))
+        self.nqk, self.nv = self.nh * self.dk, self.nh * self.dv
+        self.i_off = 2 * self.nqk + 2 * self.nv                                   # [q | k | v | g | i | f]
+        self.n_proj = self.i_off + 2 * self.nh
+        self.n_proj_pad = (self.n_proj + 7) // 8 * 8
+        self.proj = Linear(self.hidden, self.n_proj_pad, dtype)
+        self.o_proj = Linear(self.nv, self.hidden, dtype)
+        self.norm_w = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        H = self.hidden
+        return [WeightSpec("q", (self.nqk, H)), WeightSpec("k", (self.nqk, H)), WeightSpec("v", (self.nv, H)), WeightSpec("g", (self.nv, H)),
+                WeightSpec("i", (self.nh, H)), WeightSpec("f", (self.nh, H)), WeightSpec("i.b", (self.nh,), "vector", ("normal", 0.5)),
+                WeightSpec("f.b", (self.nh,), "vector", ("normal", 0.5)), WeightSpec("o", (H, self.nv)),
+                WeightSpec("norm", (self.nv,), "vector", ("ones_normal", 0.05))]
+
+    def set_weights(self, t: Dict[str, torch.Tensor]) -> None:
+        dev = t["q"].device
+        ws = [t["q"], t["k"], t["v"], t["g"], t["i"], t["f"]]
+        if self.n_proj_pad != self.n_proj:
+            ws.append(torch.zeros((self.n_proj_pad - self.n_proj, self.hidden), dtype=ws[0].dtype, device=dev))
+        b = torch.zeros(self.n_proj_pad, dtype=torch.float32, device=dev)
+        b[self.i_off: self.i_off + self.nh] = t["i.b"].float()
+        b[self.i_off + self.nh: self.i_off + 2 * self.nh] = t["f.b"].float()
+        self.proj.set(torch.cat(ws, dim=0), b)
+        self.o_proj.set(t["o"])
+        self.norm_w = t["norm"].to(torch.float32).contiguous()
+
+    def cache_need(self):
+        # S [heads, v_dim + 1, dim] (column by column; the last column is the normaliser n) and the running maximum m [heads]
+        return (CacheNeed("state", shape=(self.nh, self.dv + 1, self.dk), dtype="float32"),
+                CacheNeed("state", shape=(self.nh,), dtype="float32"))
+
+    def forward(self, x, ctx, cache):
+        S, M = cache
+        T, nqk, nv, nh = x.shape[0], self.nqk, self.nv, self.nh
+        proj = self.proj(x, ctx.ws.rows("mlstm_proj", T, self.n_proj_pad, torch.float32), out_f32=True)
+        dec = ctx.ws.rows("mlstm_decay", T, nh, torch.float32)
+        inw = ctx.ws.rows("mlstm_inw", T, nh, torch.float32)
+        floor = ctx.ws.rows("mlstm_floor", T, nh, torch.float32)
+        ops.stabilized_gates(proj, self.i_off, self.i_off + nh, self.cap, M.storage, M.read_slots,
+                             M.write_slots if M.writable else M.read_slots, ctx.entry_qstart, ctx.n_entries, dec, inw, floor, nh)
+        o = ctx.ws.rows("mlstm_o", T, nh * (self.dv + 1), torch.float32)
+        ops.matrix_state_scan_step(ctx, ops.SCAN_GATED, proj[:, :nqk], proj[:, nqk: 2 * nqk], proj[:, 2 * nqk: 2 * nqk + nv], nh, nh,
+                                   self.dk, self.dv + 1, 0, None, inw, dec, S.storage, S.read_slots,
+                                   S.write_slots if S.writable else S.read_slots, ctx.entry_qstart, out=o)
+        gated = ctx.ws.rows("mlstm_gated", T, nv, self.dtype)
+        ops.group_norm_gate(o, self.norm_w, self.eps, proj, 2 * nqk + nv, ops.GATE_SIGMOID, gated, self.dv, den_floor=floor,
+                            x_scale=self.dk ** -0.5, den_eps=self.den_eps)
+        return self.o_proj(gated, ctx.ws.rows("mlstm_branch", T, self.hidden, self.dtype))
+
+
 register_part("mixer", "decay_linear_attention", DecayLinearAttention)
+register_part("mixer", "matrix_lstm", MatrixLSTM)
 register_part("mixer", "gated_delta_rule", GatedDeltaRule)

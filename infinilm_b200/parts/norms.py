@@ -47,4 +47,10 @@ class RMSNorm(Norm):
         return out
 
 
+    def norm_add(self, resid, branch, scale, copy=None):
+        """resid (f32 [T,H]) += scale * norm(branch): the norm sits on the branch, not on the stream; `copy` receives the
+        new stream in the compute dtype."""
+        ops.norm_add(resid, branch, self.weight, self.eps, scale, copy)
+
+
 register_part("norm", "rmsnorm", RMSNorm)

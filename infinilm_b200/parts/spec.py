@@ -61,12 +61,24 @@ class WeightSpec:
     role: "matrix" (operand of a matrix product: held in the compute dtype), "vector" (norm
           weights, biases: a tensor stored in 32-bit stays 32-bit), "table" (integer table: int32).
     init: ("normal", std) | ("ones_normal", std) | ("zeros",) - used by the random-weights mode.
-    fallback: another tensor's full name used when this one is absent (a tied head)."""
+    fallback: another tensor's full name used when this one is absent (a tied head).
+    A dimension written as -1 is a size that the stored tensor itself gives (the part reads it in `set_weights`); `free` is the
+    size the random-weights mode gives it."""
     name: str                                   # local name, e.g. "q_proj.weight"
     shape: Tuple[int, ...]
     role: str = "matrix"
     init: Tuple = ("normal", 0.02)
     fallback: Optional[str] = None
+    free: Optional[int] = None
+
+    def fits(self, shape) -> bool:
+        shape = tuple(shape)
+        return len(shape) == len(self.shape) and all(w == g or (w == -1 and g >= 1) for w, g in zip(self.shape, shape))
+
+    def drawn_shape(self) -> Tuple[int, ...]:
+        if -1 in self.shape and self.free is None:
+            raise ValueError(f"tensor {self.name}: a free dimension needs a size for random weights")
+        return tuple(self.free if d == -1 else d for d in self.shape)
 
 
 @dataclass

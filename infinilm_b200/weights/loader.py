@@ -115,13 +115,13 @@ def check_against(model, source: TensorSource) -> None:
             if ws.fallback is not None and ws.fallback in have:
                 full_fb = ws.fallback
                 _, shape = source.info(full_fb)
-                if tuple(shape) != tuple(ws.shape):
+                if not ws.fits(shape):
                     wrong.append((f"{full} (taken from {full_fb})", tuple(shape), tuple(ws.shape)))
                 continue
             missing.append(full)
             continue
         dt, shape = source.info(full)
-        if tuple(shape) != tuple(ws.shape):
+        if not ws.fits(shape):
             wrong.append((full, tuple(shape), tuple(ws.shape)))
         floating = getattr(dt, "is_floating_point", None)
         if floating is not None and floating != (ws.role != "table"):

@@ -45,9 +45,9 @@ def random_tensors(cfg: ModelConfig, seed: int, device: str = "cpu", dtype: Opti
         g.manual_seed(_seed_for(seed, full))
         kind = ws.init[0]
         if kind == "zeros":
-            t = torch.zeros(ws.shape, dtype=torch.float32, device=dev)
+            t = torch.zeros(ws.drawn_shape(), dtype=torch.float32, device=dev)
         else:
-            t = torch.randn(ws.shape, generator=g, dtype=torch.float32, device=dev) * float(ws.init[1])
+            t = torch.randn(ws.drawn_shape(), generator=g, dtype=torch.float32, device=dev) * float(ws.init[1])
             if kind == "ones_normal":
                 t += 1.0
             elif kind != "normal":
