@@ -175,7 +175,7 @@ def timeline_step(args) -> int:
     raw = dict(CONFIG_05B if args.sizes == "0.5b" else CONFIG_8B)
     raw["num_hidden_layers"] = args.layers or 4
     if args.design != "default":                  # one of the pair of `--workload designs`, at the first of --design-sizes
-        pair = gopitar_pair if args.design == "gopitar" else design_pair
+        pair = {"gopitar": gopitar_pair, "somipel": somipel_pair}.get(args.design, design_pair)
         raw = pair(args.design_sizes.split(",")[0], args.layers or 4)[1 if args.design == "dense" else 0]
         raw["num_hidden_layers"] = args.layers or 4
     cfg = config_from_json(raw)
@@ -308,6 +308,31 @@ def gopitar_pair(size: str, layers: int):
     return gp, dense
 
 
+def somipel_pair(size: str, layers: int):
+    """(Somipel configuration, Gopitar configuration of the same width, depth, heads, head size, vocabulary and feed-forward
+    width: the framework's other design that mixes softmax attention over the paged cache with a matrix-state recurrence.) Of
+    every four layers the first mixes by the matrix memory, the second by attention with a bias by distance and a gate, the
+    third by attention whose values are its keys (query temperature, sink), the fourth by attention over the second's keys and
+    values; 2 kv heads, head sizes of published models (128; 64 at the small width)."""
+    W, H, d, ff, V = {"1k": (1024, 8, 64, 3072, 32000), "2k": (2048, 16, 128, 8192, 32000), "4k": (4096, 32, 128, 12288, 32000)}[size]
+    mlp = {"kind": "dense", "ff": ff}
+    def att(kv_from=None):
+        m = {"heads": H, "kv_heads": 2, "dim": d, "vdim": d, "scale": d ** -0.5, "bias_max": 4096, "bias_rows": 64}
+        if kv_from is not None:
+            m["kv_from"] = kv_from
+        return {"type": "attention", "mixer": m, "mlp": dict(mlp)}
+    def layer(i):
+        if i % 4 == 0:
+            return {"type": "mlstm", "mixer": {"heads": H, "dim": d, "vdim": d, "gate_cap": 15.0}, "mlp": dict(mlp)}
+        if i % 4 == 2:
+            return {"type": "attention_2", "mixer": {"heads": H, "kv_heads": 2, "dim": d, "vdim": d, "scale": d ** -0.5,
+                                                     "q_temp": {"coef": 0.1, "every": 512}}, "mlp": dict(mlp)}
+        return att(i - 2 if i % 4 == 3 else None)
+    sp = {"architecture": "Somipel", "vocab": V, "width": W, "norm": {"eps": 1e-5}, "residual_mult": 1.0,
+          "layers": [layer(i) for i in range(layers)]}
+    return sp, gopitar_pair(size, layers)[0]
+
+
 class OpTimer:
     """Brackets every kernel wrapper of `infinilm_b200.ops`, every library product of `Linear` and the library's grouped
     product with CUDA events on the launching stream, for steps that run eagerly; `table()` gives microseconds and calls per name."""
@@ -327,7 +352,7 @@ class OpTimer:
             e1.record()
             lab = label or name
             if lab == "matrix_state_scan":
-                lab += (" delta" if a[0] == 1 else " decay") + (" single" if k.get("single") else "")
+                lab += {1: " delta", 3: " gated"}.get(a[0], " decay") + (" single" if k.get("single") else "") + (" segmented" if k.get("seg_len") else "")
             elif lab == "short_conv":
                 lab += f"[{a[10]}x{a[11]}]"
             if lab == "linear":
@@ -349,7 +374,8 @@ class OpTimer:
         for name in ("embed", "embed_pair_pos", "add_rmsnorm", "swiglu", "rope_store", "attention_plain", "attention_decode",
                      "attention_prefill", "attention_prefill_tc5", "gemm_skinny", "gemm_skinny_resid", "gemm_skinny_rope", "gemm_mid",
                      "gemm_tc5", "latent_norm_store", "moe_route", "moe_sort", "moe_combine", "gather_rows", "gemm_grouped", "short_conv",
-                     "short_conv_state", "delta_prep", "matrix_state_scan", "group_norm_gate", "head_gate", "scaled_sum", "softcap", "silu_cols"):
+                     "short_conv_state", "delta_prep", "matrix_state_scan", "group_norm_gate", "head_gate", "scaled_sum", "softcap", "silu_cols", "norm_add", "cast_rows",
+                     "qk_norm_store", "gate_pack", "stabilized_gates"):
             self._wrap(ops, name)
         self._wrap(Linear, "__call__", "linear")
         if hasattr(F, "grouped_mm"):
@@ -388,7 +414,8 @@ def run_designs(args) -> int:
         rec = {"workload": "designs", "size": size, "layers": L, "dtype": "bf16", "data": "synthetic", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src}}
         family = getattr(args, "design_family", "nirozen")
         rec["design"] = family
-        for which, raw in zip((family, "dense_gqa"), gopitar_pair(size, L) if family == "gopitar" else design_pair(size, L)):
+        pair = {"gopitar": gopitar_pair, "somipel": somipel_pair}.get(family, design_pair)
+        for which, raw in zip((family, "gopitar" if family == "somipel" else "dense_gqa"), pair(size, L)):
             cfg = config_from_json(raw)
             B = 64
             eng = Engine.from_tensors(cfg, random_tensors(cfg, 0, "cuda:0"), dtype="bfloat16", page_size=PAGE,
@@ -489,10 +516,10 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--no-graph", action="store_true", help="do not replay decode steps as CUDA graphs")
     ap.add_argument("--points", type=str, default="1,64", help="batch sizes of the extra decode points")
-    ap.add_argument("--design", choices=["default", "nirozen", "gopitar", "dense"], default="default",
+    ap.add_argument("--design", choices=["default", "nirozen", "gopitar", "somipel", "dense"], default="default",
                     help="--timeline: the step of one of the pair of --workload designs instead of the benchmark model")
-    ap.add_argument("--design-family", choices=["nirozen", "gopitar"], default="nirozen",
-                    help="--workload designs: which design stands beside the dense GQA model of equal size")
+    ap.add_argument("--design-family", choices=["nirozen", "gopitar", "somipel"], default="nirozen",
+                    help="--workload designs: which design stands beside the dense GQA model of equal size (somipel: beside gopitar)")
     ap.add_argument("--design-sizes", type=str, default="1k,2k", help="--workload designs: layer sizes to run (1k, 2k, 4k)")
     ap.add_argument("--workload", choices=["default", "long_context", "continuous", "designs"], default="default",
                     help="default: the benchmark line. long_context: 8 requests x 16,384-token prompts at 8B sizes, prompt "

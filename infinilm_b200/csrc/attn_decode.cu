@@ -165,7 +165,8 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ entry_kvlen, int nh, int nkv,
     float scale_log2, int window, int pages_per_split, int n_splits, float* __restrict__ o_part,
     float* __restrict__ ml_part, const __grid_constant__ CUtensorMap kv_map, const __grid_constant__ CUtensorMap kv_page_map,
-    int use_tma, int* __restrict__ status, __nv_bfloat16* __restrict__ out_direct, const float* __restrict__ sink) {
+    int use_tma, int* __restrict__ status, __nv_bfloat16* __restrict__ out_direct, const float* __restrict__ sink,
+    const float* __restrict__ dist_bias, int dist_far) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     // Lengths, block tables and the pages of earlier tokens do not come from the kernel before this one (it writes q and
@@ -279,15 +280,30 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
     at_load_q(qf, [&](int r) { return r < rows_valid ? qbase + (size_t)(head0 + r) * AT_HD : nullptr; }, lane);
 
     // One page: scores, online softmax, P.V. `qk` fills s[2][4] from the K tile, `pv` adds P.V from the V tile.
+    // A bias by distance (dist_bias[head][min(n, dist_far)], n = kvlen - 1 - key): this thread's two rows of the table, and
+    // what they hold from dist_far on - a page that lies wholly beyond it (most pages of a long context) adds a constant.
+    const float* db_row[2] = {nullptr, nullptr};
+    float db_far[2] = {0.f, 0.f};
+    if (dist_bias) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int r = min((lane >> 2) + 8 * h, rows_valid - 1);
+            db_row[h] = dist_bias + (size_t)(head0 + r) * (dist_far + 1);
+            db_far[h] = db_row[h][dist_far] * 1.4426950408889634f;
+        }
+    }
     auto softmax_page = [&](float (&s)[2][4], int it, uint32_t (&pf)[4]) {
         const int key0 = (p0 + warp + it * AD_WARPS) * AD_PAGE + (lane & 3) * 2;
         const int hi = ((bad_pages >> (it & 31)) & 1) ? 0 : kvlen;
+        const bool db_near = dist_bias && kvlen - 1 - ((p0 + warp + it * AD_WARPS) * AD_PAGE + AD_PAGE - 1) < dist_far;
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const int key = key0 + nt * 8 + (j & 1);
-                s[nt][j] = (key >= lo && key < hi) ? s[nt][j] * scale_log2 : -INFINITY;
+                float v = s[nt][j] * scale_log2;
+                if (dist_bias) v += db_near ? db_row[j >> 1][max(0, min(kvlen - 1 - key, dist_far))] * 1.4426950408889634f : db_far[j >> 1];
+                s[nt][j] = (key >= lo && key < hi) ? v : -INFINITY;
             }
 #pragma unroll
         for (int h = 0; h < 2; ++h) {             // h = 0: row lane/4, h = 1: row lane/4 + 8
@@ -492,7 +508,8 @@ __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* o_p
 static int ad_launch(const void* qkv, int row_stride, void* out, const void* cache, const int* block_table, int bt_stride,
                      const int* entry_kvlen, int n_decode, int nh, int nkv, float scale, int window, int pages_per_split,
                      int n_splits, float* o_part, float* ml_part, cudaStream_t stream, const CUtensorMap* kv_map = nullptr,
-                     int* status = nullptr, const float* sink = nullptr, int v_is_k = 0) {
+                     int* status = nullptr, const float* sink = nullptr, int v_is_k = 0, const float* dist_bias = nullptr,
+                     int dist_far = 0) {
     static CUtensorMap no_map;                    // passed when there is no map: the kernel does not look at it
     int use_tma = (AD_TMA_OK && kv_map && status) ? 1 : 0;
     auto filled = [&](int i) {                    // maps behind the first are all zero where the driver did not take them
@@ -518,7 +535,7 @@ static int ad_launch(const void* qkv, int row_stride, void* out, const void* cac
     IL_LAUNCH(attn_decode_kernel, grid, AD_WARPS * 32, smem_bytes, stream,
         (const __nv_bfloat16*)qkv, row_stride, (const __nv_bfloat16*)cache, block_table, bt_stride, entry_kvlen, nh, nkv,
         scale * 1.4426950408889634f, window, pages_per_split, n_splits, o_part, ml_part, use_tma ? *kv_map : no_map, page_map, use_tma, status,
-        n_splits == 1 ? (__nv_bfloat16*)out : (__nv_bfloat16*)nullptr, sink);
+        n_splits == 1 ? (__nv_bfloat16*)out : (__nv_bfloat16*)nullptr, sink, dist_bias, dist_far);
     if (n_splits == 1) {                          // every row is final as the attention kernel leaves it: no merge
         IL_LAUNCH_CHECK();
         return IL_OK;
@@ -562,13 +579,15 @@ IL_EXPORT int il_attn_decode_resident_blocks_shared() { return ad_resident_block
 IL_EXPORT int il_attn_decode(const void* qkv, int row_stride, void* out, const void* cache, const int* block_table,
                              int bt_stride, const int* entry_kvlen, int page_size, int n_decode, int nh, int nkv, int hd,
                              float scale, int window, int pages_per_split, int n_splits, float* o_part, float* ml_part,
-                             const void* kv_map, int* status, const float* sink, int v_is_k, cudaStream_t stream) {
+                             const void* kv_map, int* status, const float* sink, int v_is_k, const float* dist_bias, int dist_far,
+                             cudaStream_t stream) {
     if (n_decode <= 0) return IL_OK;
+    if (dist_bias && dist_far < 0) return IL_BAD_ARG;
     if (hd != HEAD_DIM || page_size != AD_PAGE) return IL_UNSUPPORTED;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || pages_per_split < 0 || n_splits <= 0) return IL_BAD_ARG;
     if (n_splits > AD_MAX_SPLITS) return IL_UNSUPPORTED;
     return ad_launch(qkv, row_stride, out, cache, block_table, bt_stride, entry_kvlen, n_decode, nh, nkv, scale, window,
-                     pages_per_split, n_splits, o_part, ml_part, stream, (const CUtensorMap*)kv_map, status, sink, v_is_k);
+                     pages_per_split, n_splits, o_part, ml_part, stream, (const CUtensorMap*)kv_map, status, sink, v_is_k, dist_bias, dist_far);
 }
 
 // Writes four tensor maps (4 x 128 bytes at `out_maps`) of one layer's cache, [pages][2][kv heads][16][head_dim] bfloat16:

@@ -32,7 +32,8 @@ __global__ void __launch_bounds__(AP_WARPS * 32) attn_prefill_kernel(
     const __nv_bfloat16* __restrict__ qkv, int row_stride, __nv_bfloat16* __restrict__ out,
     const __nv_bfloat16* __restrict__ cache, const int* __restrict__ block_table, int bt_stride,
     const int* __restrict__ entry_qstart, const int* __restrict__ entry_kvlen, int first_entry, int n_entries, int nh,
-    int nkv, float scale_log2, int window, int tpt, const float* __restrict__ sink) {
+    int nkv, float scale_log2, int window, int tpt, const float* __restrict__ sink, const float* __restrict__ dist_bias, int dist_far,
+    float inv_scale) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int G = nh / nkv;
     const int g = blockIdx.y;
@@ -73,6 +74,15 @@ __global__ void __launch_bounds__(AP_WARPS * 32) attn_prefill_kernel(
         qptr[h] = rvalid[h] ? qkv + (size_t)(tok0 + tl) * row_stride + (size_t)(g * G + hh) * AT_HD : nullptr;
         optr[h] = rvalid[h] ? out + (size_t)(tok0 + tl) * nh * AT_HD + (size_t)(g * G + hh) * AT_HD : nullptr;
         if (!rvalid[h]) { rpos[h] = -1; rlo[h] = 0; }
+    }
+    const float* db_row[2] = {nullptr, nullptr};  // this thread's two rows of the bias table, and their value from dist_far on
+    float db_far[2] = {0.f, 0.f};
+    if (dist_bias) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            db_row[h] = dist_bias + (size_t)rhead[h] * (dist_far + 1);
+            db_far[h] = db_row[h][dist_far] * inv_scale;
+        }
     }
     uint32_t qf[AT_KSTEPS][4];
     {
@@ -165,13 +175,16 @@ __global__ void __launch_bounds__(AP_WARPS * 32) attn_prefill_kernel(
             if (!use[p]) continue;
             const int k0 = key_base + p * AP_PAGE;
             const bool need_mask = (k0 + AP_PAGE - 1 > wmin_pos) || (k0 < wmax_lo);
+            // a bias by distance joins the unscaled score as bias / scale; a page wholly beyond dist_far adds a constant per row
+            const bool db_near = dist_bias && wmin_pos - (k0 + AP_PAGE - 1) < dist_far;
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int h = j >> 1;
+                    const int key = k0 + nt * 8 + (lane & 3) * 2 + (j & 1);
+                    if (dist_bias) s[p][nt][j] += db_near ? db_row[h][max(0, min(rpos[h] - key, dist_far))] * inv_scale : db_far[h];
                     if (need_mask) {
-                        const int key = k0 + nt * 8 + (lane & 3) * 2 + (j & 1);
                         if (!(key <= rpos[h] && key >= rlo[h])) s[p][nt][j] = -INFINITY;
                     }
                     mx[h] = fmaxf(mx[h], s[p][nt][j]);
@@ -239,8 +252,9 @@ __global__ void __launch_bounds__(AP_WARPS * 32) attn_prefill_kernel(
 IL_EXPORT int il_attn_prefill(const void* qkv, int row_stride, void* out, const void* cache, const int* block_table,
                               int bt_stride, const int* entry_qstart, const int* entry_kvlen, int page_size,
                               int first_entry, int n_entries, int n_tiles_total, int nh, int nkv, int hd, float scale,
-                              int window, const float* sink, cudaStream_t stream) {
+                              int window, const float* sink, const float* dist_bias, int dist_far, cudaStream_t stream) {
     if (n_tiles_total <= 0 || first_entry >= n_entries) return IL_OK;
+    if (dist_bias && (dist_far < 0 || !(scale > 0.f))) return IL_BAD_ARG;
     if (hd != HEAD_DIM || page_size != AP_PAGE) return IL_UNSUPPORTED;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0) return IL_BAD_ARG;
     const int G = nh / nkv;
@@ -254,7 +268,8 @@ IL_EXPORT int il_attn_prefill(const void* qkv, int row_stride, void* out, const 
     dim3 grid(n_tiles_total, nkv);
     attn_prefill_kernel<<<grid, AP_WARPS * 32, AP_SMEM, stream>>>(
         (const __nv_bfloat16*)qkv, row_stride, (__nv_bfloat16*)out, (const __nv_bfloat16*)cache, block_table, bt_stride,
-        entry_qstart, entry_kvlen, first_entry, n_entries, nh, nkv, scale * 1.4426950408889634f, window, AP_ROWS / G, sink);
+        entry_qstart, entry_kvlen, first_entry, n_entries, nh, nkv, scale * 1.4426950408889634f, window, AP_ROWS / G, sink, dist_bias, dist_far,
+        1.f / scale);
     IL_LAUNCH_CHECK();
     return IL_OK;
 }

@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(PT_THREADS, PT_BLOCKS_PER_SM) attn_prefill_tc5
     const __grid_constant__ CUtensorMap kv_map, const __nv_bfloat16* __restrict__ qkv, int row_stride,
     __nv_bfloat16* __restrict__ out, const int* __restrict__ block_table, int bt_stride, const int* __restrict__ entry_qstart,
     const int* __restrict__ entry_kvlen, int first_entry, int n_entries, int nh, int nkv, float scale_log2, int window, int tpt,
-    int* __restrict__ status, const float* __restrict__ sink) {
+    int* __restrict__ status, const float* __restrict__ sink, const float* __restrict__ dist_bias, int dist_far, float inv_scale) {
     extern __shared__ __align__(1024) unsigned char smem[];
     if (t5_smem(smem) & 1023u) {                  // the swizzled tiles need 1 KB alignment; dynamic shared memory starts on it
         if (threadIdx.x == 0) atomicExch(status, 30);
@@ -274,6 +274,10 @@ __global__ void __launch_bounds__(PT_THREADS, PT_BLOCKS_PER_SM) attn_prefill_tc5
         unsigned char* p_row = p_smem + r * 128;
         float m = -INFINITY, l = 0.f;
         bool ok = true;
+        // a bias by distance: this row's line of the table (bias[head][min(n, dist_far)]) and its value from dist_far on,
+        // both as they join the unscaled score (bias / scale)
+        const float* db_row = dist_bias ? dist_bias + (size_t)(g * G + hh) * (dist_far + 1) : nullptr;
+        const float db_far = dist_bias ? db_row[dist_far] * inv_scale : 0.f;
         for (int j = 0; j < n_tiles; ++j) {
             const int b = j & 1;
             if (!t5_mbar_wait(s_full0 + 8 * b, (uint32_t)(j >> 1) & 1u, PT_SPIN)) { atomicExch(status, 36); ok = false; break; }
@@ -287,6 +291,16 @@ __global__ void __launch_bounds__(PT_THREADS, PT_BLOCKS_PER_SM) attn_prefill_tc5
             __syncwarp();
             if (lane == 0) t5_mbar_arrive(s_free0 + 8 * b);
             const int kb = (page_first + j * PT_TILE_PAGES) * PT_PAGE;
+            if (dist_bias) {
+                if (rpos - (kb + PT_KEYS - 1) >= dist_far) {  // the whole tile lies beyond dist_far for this row: a constant
+#pragma unroll
+                    for (int c = 0; c < PT_KEYS; ++c) sv[c] = __float_as_uint(__uint_as_float(sv[c]) + db_far);
+                } else {
+#pragma unroll
+                    for (int c = 0; c < PT_KEYS; ++c)
+                        sv[c] = __float_as_uint(fmaf(db_row[max(0, min(rpos - kb - c, dist_far))], inv_scale, __uint_as_float(sv[c])));
+                }
+            }
             if (kb + PT_KEYS - 1 > rpos || kb < rlo) {        // the tile touches this row's causal or window edge
 #pragma unroll
                 for (int c = 0; c < PT_KEYS; ++c) {
@@ -399,8 +413,9 @@ IL_EXPORT int il_attn_prefill_tc5_rows() { return PT_ROWS; }
 IL_EXPORT int il_attn_prefill_tc5(const void* qkv, int row_stride, void* out, const void* kv_map, const int* block_table,
                                   int bt_stride, const int* entry_qstart, const int* entry_kvlen, int page_size, int first_entry,
                                   int n_entries, int n_tiles_total, int nh, int nkv, int hd, float scale, int window, int* status,
-                                  const float* sink, cudaStream_t stream) {
+                                  const float* sink, const float* dist_bias, int dist_far, cudaStream_t stream) {
     if (n_tiles_total <= 0 || first_entry >= n_entries) return IL_OK;
+    if (dist_bias && dist_far < 0) return IL_BAD_ARG;
     if (hd != HEAD_DIM || page_size != PT_PAGE || !kv_map || !status) return IL_UNSUPPORTED;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0) return IL_BAD_ARG;
     const int G = nh / nkv;
@@ -421,7 +436,7 @@ IL_EXPORT int il_attn_prefill_tc5(const void* qkv, int row_stride, void* out, co
     dim3 grid(n_tiles_total, nkv);
     attn_prefill_tc5_kernel<<<grid, PT_THREADS, PT_SMEM, stream>>>(
         map, (const __nv_bfloat16*)qkv, row_stride, (__nv_bfloat16*)out, block_table, bt_stride, entry_qstart, entry_kvlen,
-        first_entry, n_entries, nh, nkv, scale * 1.4426950408889634f, window, PT_ROWS / G, status, sink);
+        first_entry, n_entries, nh, nkv, scale * 1.4426950408889634f, window, PT_ROWS / G, status, sink, dist_bias, dist_far, 1.f / scale);
     IL_LAUNCH_CHECK();
     return IL_OK;
 }

@@ -364,7 +364,7 @@ def attention_decode(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, 
                      entry_kvlen: torch.Tensor, n_decode: int, page_size: int, n_heads: int, n_kv_heads: int,
                      head_dim: int, scale: float, window: Optional[int], pages_per_split: int, n_splits: int,
                      o_part: torch.Tensor, ml_part: torch.Tensor, kv_map: Optional[torch.Tensor] = None,
-                     sink: Optional[torch.Tensor] = None, v_is_k: bool = False) -> None:
+                     sink: Optional[torch.Tensor] = None, v_is_k: bool = False, dist_bias: Optional[torch.Tensor] = None) -> None:
     """bfloat16 split-KV attention of token rows [0, n_decode) (entry i = row i, one token each), then the merge of
     the splits (a second launch; with n_splits = 1 there is none and the attention kernel writes `out` itself). A row whose length is 0 gets zeros; a block-table entry below 0 is never followed.
     pages_per_split 0: each request's pages are divided evenly over the n_splits splits.
@@ -372,8 +372,9 @@ def attention_decode(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, 
     v_is_k: the caller vouches that the V plane of every page repeats its K plane (a latent that is key and value at once);
     with a tensor map only the K plane is then read, half the bytes.
     Scratch: o_part float32 [n_decode*heads*n_splits*head_dim], ml_part float32 [n_decode*heads*n_splits*2]."""
-    _need_cuda(qkv, out, cache, block_table, entry_kvlen, o_part, ml_part, sink)
+    _need_cuda(qkv, out, cache, block_table, entry_kvlen, o_part, ml_part, sink, dist_bias)
     _check_sink(sink, n_heads)
+    _check_dist_bias(dist_bias, n_heads)      # float32 [heads, far + 1]: added to the scaled score of a key n positions back
     if qkv.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
         raise KernelError("attention_decode: bfloat16 tensors")
     if o_part is None or ml_part is None or o_part.dtype != torch.float32 or ml_part.dtype != torch.float32:
@@ -388,13 +389,14 @@ def attention_decode(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, 
     _contig("qkv", qkv), _contig("out", out), _contig("cache", cache), _contig("block_table", block_table)
     f = _fn("attn_decode", "il_attn_decode", [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int,
                                               _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_void_p,
-                                              _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p], defines={"HEAD_DIM": head_dim})
+                                              _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p],
+            defines={"HEAD_DIM": head_dim})
     if kv_map is not None and (kv_map.is_cuda or kv_map.dtype != torch.uint8 or kv_map.numel() != KV_MAP_BYTES):
         raise KernelError("attention_decode: kv_map must be the host tensor kv_tensor_map returned")
     _check(f(_ptr(qkv), qkv.shape[1], _ptr(out), _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(entry_kvlen),
              page_size, n_decode, n_heads, n_kv_heads, head_dim, scale, int(window or 0), pages_per_split, n_splits,
              _ptr(o_part), _ptr(ml_part), _ptr(kv_map), _ptr(stream_status(qkv.device)) if kv_map is not None else _c_void_p(0),
-             _ptr(sink), 1 if v_is_k else 0, _stream()), "attention_decode")
+             _ptr(sink), 1 if v_is_k else 0, _ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[1] - 1, _stream()), "attention_decode")
     if n_splits > 1:
         count_launches(1)                         # the merge kernel (a single split needs none: the attention kernel finishes the rows)
 
@@ -440,11 +442,12 @@ def kv_tensor_map(cache: torch.Tensor) -> Optional[torch.Tensor]:
 def attention_prefill(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                       entry_qstart: torch.Tensor, entry_kvlen: torch.Tensor, first_entry: int, n_entries: int,
                       n_tiles_total: int, page_size: int, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
-                      window: Optional[int], sink: Optional[torch.Tensor] = None) -> None:
+                      window: Optional[int], sink: Optional[torch.Tensor] = None, dist_bias: Optional[torch.Tensor] = None) -> None:
     """bfloat16 causal attention of the tokens of entries [first_entry, n_entries) over their cache pages.
     n_tiles_total = sum over those entries of ceil(q_len / (64 // (heads/kv_heads)))."""
-    _need_cuda(qkv, out, cache, block_table, entry_qstart, entry_kvlen, sink)
+    _need_cuda(qkv, out, cache, block_table, entry_qstart, entry_kvlen, sink, dist_bias)
     _check_sink(sink, n_heads)
+    _check_dist_bias(dist_bias, n_heads)
     if qkv.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
         raise KernelError("attention_prefill: bfloat16 tensors")
     if out.shape != (qkv.shape[0], n_heads * head_dim):
@@ -452,10 +455,10 @@ def attention_prefill(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor,
     _contig("qkv", qkv), _contig("out", out), _contig("cache", cache), _contig("block_table", block_table)
     f = _fn("attn_prefill", "il_attn_prefill", [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p,
                                                 _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
-                                                _c_int, _c_void_p, _c_void_p], defines={"HEAD_DIM": head_dim})
+                                                _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p], defines={"HEAD_DIM": head_dim})
     _check(f(_ptr(qkv), qkv.shape[1], _ptr(out), _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(entry_qstart),
              _ptr(entry_kvlen), page_size, first_entry, n_entries, n_tiles_total, n_heads, n_kv_heads, head_dim, scale,
-             int(window or 0), _ptr(sink), _stream()), "attention_prefill")
+             int(window or 0), _ptr(sink), _ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[1] - 1, _stream()), "attention_prefill")
 
 
 _tc5_prefill_rows = {}
@@ -493,11 +496,12 @@ def _has_third_map(kv_map: torch.Tensor) -> bool:
 def attention_prefill_tc5(qkv: torch.Tensor, out: torch.Tensor, kv_map: torch.Tensor, block_table: torch.Tensor,
                           entry_qstart: torch.Tensor, entry_kvlen: torch.Tensor, first_entry: int, n_entries: int,
                           n_tiles_total: int, page_size: int, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
-                          window: Optional[int], sink: Optional[torch.Tensor] = None) -> None:
+                          window: Optional[int], sink: Optional[torch.Tensor] = None, dist_bias: Optional[torch.Tensor] = None) -> None:
     """The same attention as `attention_prefill`, on tcgen05 tensor cores with tensor memory; `kv_map` is the cache's
     tensor map (`kv_tensor_map`). n_tiles_total = sum over the entries of ceil(q_len / (prefill_tc5_rows(head_dim) // (heads/kv_heads)))."""
-    _need_cuda(qkv, out, block_table, entry_qstart, entry_kvlen, sink)
+    _need_cuda(qkv, out, block_table, entry_qstart, entry_kvlen, sink, dist_bias)
     _check_sink(sink, n_heads)
+    _check_dist_bias(dist_bias, n_heads)
     if qkv.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("attention_prefill_tc5: bfloat16 tensors")
     if not _has_third_map(kv_map):
@@ -507,10 +511,11 @@ def attention_prefill_tc5(qkv: torch.Tensor, out: torch.Tensor, kv_map: torch.Te
     _contig("qkv", qkv), _contig("out", out), _contig("block_table", block_table)
     f = _fn("attn_prefill_tc5", "il_attn_prefill_tc5",
             [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
-             _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p, _c_void_p, _c_void_p], defines={"HEAD_DIM": head_dim})
+             _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p], defines={"HEAD_DIM": head_dim})
     _check(f(_ptr(qkv), qkv.shape[1], _ptr(out), _c_void_p(kv_map.data_ptr() + 256), _ptr(block_table), block_table.shape[1],
              _ptr(entry_qstart), _ptr(entry_kvlen), page_size, first_entry, n_entries, n_tiles_total, n_heads, n_kv_heads,
-             head_dim, scale, int(window or 0), _ptr(stream_status(qkv.device)), _ptr(sink), _stream()), "attention_prefill_tc5")
+             head_dim, scale, int(window or 0), _ptr(stream_status(qkv.device)), _ptr(sink), _ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[1] - 1,
+             _stream()), "attention_prefill_tc5")
 
 
 SKINNY_MAX_ROWS = 16

@@ -47,7 +47,7 @@ class PagedAttend:
 
     def fast_ok(self, page_size: int) -> bool:
         return (self.dtype == torch.bfloat16 and page_size == self.FAST_PAGE and self.nh // self.nkv <= self.FAST_MAX_GROUP
-                and not self.force_plain and self.hd % 16 == 0 and 16 <= self.hd <= 256 and self.dist_bias is None)
+                and not self.force_plain and self.hd % 16 == 0 and 16 <= self.hd <= 256)
 
     def decode_splits(self, base: int, max_pages: int, resident: int) -> int:
         """Splits of the keys for `base` blocks per split: as many as fill the wanted share of one wave of blocks
@@ -82,7 +82,7 @@ class PagedAttend:
                                  self.nh, self.nkv, self.hd, self.scale, self.window, 0, n_splits,
                                  ctx.ws.flat("attn_o_part", rows * self.hd, torch.float32),
                                  ctx.ws.flat("attn_ml_part", rows * 2, torch.float32), kv_map=cache.tma_map, sink=self.sink,
-                                 v_is_k=v_is_k)
+                                 v_is_k=v_is_k, dist_bias=self.dist_bias)
         if E > n_dec:
             # prompt portions: on tcgen05 with tensor memory where the head size has that kernel (64, 128, 256) and the cache
             # its tensor map; else the mma.sync kernel. The tile is 128 (64) rows = tokens x heads of a kv head.
@@ -93,11 +93,11 @@ class PagedAttend:
             if tc5:
                 ops.attention_prefill_tc5(qkv, out, cache.tma_map, cache.block_table, ctx.entry_qstart, ctx.entry_kvlen,
                                           n_dec, E, n_tiles, cache.page_size, self.nh, self.nkv, self.hd, self.scale,
-                                          self.window, sink=self.sink)
+                                          self.window, sink=self.sink, dist_bias=self.dist_bias)
             else:
                 ops.attention_prefill(qkv, out, cache.storage, cache.block_table, ctx.entry_qstart, ctx.entry_kvlen,
                                       n_dec, E, n_tiles, cache.page_size, self.nh, self.nkv, self.hd, self.scale,
-                                      self.window, sink=self.sink)
+                                      self.window, sink=self.sink, dist_bias=self.dist_bias)
 
 
 class Attention(Mixer):
