@@ -280,16 +280,17 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
     at_load_q(qf, [&](int r) { return r < rows_valid ? qbase + (size_t)(head0 + r) * AT_HD : nullptr; }, lane);
 
     // One page: scores, online softmax, P.V. `qk` fills s[2][4] from the K tile, `pv` adds P.V from the V tile.
-    // A bias by distance (dist_bias[head][min(n, dist_far)], n = kvlen - 1 - key): this thread's two rows of the table, and
-    // what they hold from dist_far on - a page that lies wholly beyond it (most pages of a long context) adds a constant.
+    // A bias by distance (dist_bias[min(n, dist_far)][head], n = kvlen - 1 - key; the heads of one distance lie together, as
+    // the rows of a tile do): this thread's two columns of the table, and what they hold from dist_far on - a page that lies
+    // wholly beyond it (most pages of a long context) adds a constant.
     const float* db_row[2] = {nullptr, nullptr};
     float db_far[2] = {0.f, 0.f};
     if (dist_bias) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int r = min((lane >> 2) + 8 * h, rows_valid - 1);
-            db_row[h] = dist_bias + (size_t)(head0 + r) * (dist_far + 1);
-            db_far[h] = db_row[h][dist_far] * 1.4426950408889634f;
+            db_row[h] = dist_bias + head0 + r;
+            db_far[h] = db_row[h][(size_t)dist_far * nh] * 1.4426950408889634f;
         }
     }
     auto softmax_page = [&](float (&s)[2][4], int it, uint32_t (&pf)[4]) {
@@ -302,7 +303,7 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
             for (int j = 0; j < 4; ++j) {
                 const int key = key0 + nt * 8 + (j & 1);
                 float v = s[nt][j] * scale_log2;
-                if (dist_bias) v += db_near ? db_row[j >> 1][max(0, min(kvlen - 1 - key, dist_far))] * 1.4426950408889634f : db_far[j >> 1];
+                if (dist_bias) v += db_near ? db_row[j >> 1][(size_t)max(0, min(kvlen - 1 - key, dist_far)) * nh] * 1.4426950408889634f : db_far[j >> 1];
                 s[nt][j] = (key >= lo && key < hi) ? v : -INFINITY;
             }
 #pragma unroll

@@ -7,7 +7,7 @@
 //
 // The query of token t is at absolute position p = tok_pos[t] of its request and sees cache
 // positions max(0, p - window + 1) .. p (window <= 0: all). Query head j reads kv head j / (nh / nkv).
-// With `dist_bias` (f32 [heads][dist_far + 1]) the scaled score of a key n positions back gets dist_bias[head][min(n, dist_far)]
+// With `dist_bias` (f32 [dist_far + 1][heads]) the scaled score of a key n positions back gets dist_bias[min(n, dist_far)][head]
 // added: a learned bias by distance that is constant from dist_far on.
 #include "common.cuh"
 
@@ -48,7 +48,7 @@ __global__ void attn_plain_kernel(const TA* __restrict__ qkv, int row_stride, TA
             if (d < hd) dot += q[r] * il_to_f(krow[d]);
         }
         dot = il_warp_sum(dot) * scale;
-        if (dist_bias) dot += dist_bias[(size_t)j * (dist_far + 1) + min(pos - kp, dist_far)];
+        if (dist_bias) dot += dist_bias[(size_t)min(pos - kp, dist_far) * nh + j];
         const float mn = fmaxf(m, dot);
         const float corr = expf(m - mn);  // exp(-inf) = 0 on the first key
         const float p = expf(dot - mn);

@@ -75,13 +75,13 @@ __global__ void __launch_bounds__(AP_WARPS * 32) attn_prefill_kernel(
         optr[h] = rvalid[h] ? out + (size_t)(tok0 + tl) * nh * AT_HD + (size_t)(g * G + hh) * AT_HD : nullptr;
         if (!rvalid[h]) { rpos[h] = -1; rlo[h] = 0; }
     }
-    const float* db_row[2] = {nullptr, nullptr};  // this thread's two rows of the bias table, and their value from dist_far on
+    const float* db_row[2] = {nullptr, nullptr};  // this thread's two columns of the bias table [dist_far + 1][heads], and their value from dist_far on
     float db_far[2] = {0.f, 0.f};
     if (dist_bias) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            db_row[h] = dist_bias + (size_t)rhead[h] * (dist_far + 1);
-            db_far[h] = db_row[h][dist_far] * inv_scale;
+            db_row[h] = dist_bias + rhead[h];
+            db_far[h] = db_row[h][(size_t)dist_far * nh] * inv_scale;
         }
     }
     uint32_t qf[AT_KSTEPS][4];
@@ -183,7 +183,7 @@ __global__ void __launch_bounds__(AP_WARPS * 32) attn_prefill_kernel(
                 for (int j = 0; j < 4; ++j) {
                     const int h = j >> 1;
                     const int key = k0 + nt * 8 + (lane & 3) * 2 + (j & 1);
-                    if (dist_bias) s[p][nt][j] += db_near ? db_row[h][max(0, min(rpos[h] - key, dist_far))] * inv_scale : db_far[h];
+                    if (dist_bias) s[p][nt][j] += db_near ? db_row[h][(size_t)max(0, min(rpos[h] - key, dist_far)) * nh] * inv_scale : db_far[h];
                     if (need_mask) {
                         if (!(key <= rpos[h] && key >= rlo[h])) s[p][nt][j] = -INFINITY;
                     }

@@ -274,10 +274,11 @@ __global__ void __launch_bounds__(PT_THREADS, PT_BLOCKS_PER_SM) attn_prefill_tc5
         unsigned char* p_row = p_smem + r * 128;
         float m = -INFINITY, l = 0.f;
         bool ok = true;
-        // a bias by distance: this row's line of the table (bias[head][min(n, dist_far)]) and its value from dist_far on,
+        // a bias by distance: this row's column of the table (bias[min(n, dist_far)][head]: a warp's rows are the heads of a few
+        // neighbouring tokens, so what it reads for one key lies together) and its value from dist_far on,
         // both as they join the unscaled score (bias / scale)
-        const float* db_row = dist_bias ? dist_bias + (size_t)(g * G + hh) * (dist_far + 1) : nullptr;
-        const float db_far = dist_bias ? db_row[dist_far] * inv_scale : 0.f;
+        const float* db_row = dist_bias ? dist_bias + g * G + hh : nullptr;
+        const float db_far = dist_bias ? db_row[(size_t)dist_far * nh] * inv_scale : 0.f;
         for (int j = 0; j < n_tiles; ++j) {
             const int b = j & 1;
             if (!t5_mbar_wait(s_full0 + 8 * b, (uint32_t)(j >> 1) & 1u, PT_SPIN)) { atomicExch(status, 36); ok = false; break; }
@@ -295,10 +296,14 @@ __global__ void __launch_bounds__(PT_THREADS, PT_BLOCKS_PER_SM) attn_prefill_tc5
                 if (rpos - (kb + PT_KEYS - 1) >= dist_far) {  // the whole tile lies beyond dist_far for this row: a constant
 #pragma unroll
                     for (int c = 0; c < PT_KEYS; ++c) sv[c] = __float_as_uint(__uint_as_float(sv[c]) + db_far);
+                } else if (rpos - kb <= dist_far && rpos - kb >= PT_KEYS - 1) {      // every key of the tile has a line of its own
+                    const float* dbp = db_row + (size_t)(rpos - kb) * nh;
+#pragma unroll
+                    for (int c = 0; c < PT_KEYS; ++c) sv[c] = __float_as_uint(fmaf(dbp[-(ptrdiff_t)c * nh], inv_scale, __uint_as_float(sv[c])));
                 } else {
 #pragma unroll
                     for (int c = 0; c < PT_KEYS; ++c)
-                        sv[c] = __float_as_uint(fmaf(db_row[max(0, min(rpos - kb - c, dist_far))], inv_scale, __uint_as_float(sv[c])));
+                        sv[c] = __float_as_uint(fmaf(db_row[(size_t)max(0, min(rpos - kb - c, dist_far)) * nh], inv_scale, __uint_as_float(sv[c])));
                 }
             }
             if (kb + PT_KEYS - 1 > rpos || kb < rlo) {        // the tile touches this row's causal or window edge

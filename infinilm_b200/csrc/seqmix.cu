@@ -800,11 +800,12 @@ __global__ void __launch_bounds__(SG_TOK) stabilized_gates_kernel(const float* z
                                                                   const int* __restrict__ write_slots, const int* __restrict__ qstart,
                                                                   float* __restrict__ decay, float* __restrict__ inw,
                                                                   float* __restrict__ floor_, int H, int e0) {
-    __shared__ float si[SG_TOK], sf[SG_TOK], sm_[SG_TOK + 1];
+    __shared__ __align__(16) float si[SG_TOK], sf[SG_TOK], sm_[SG_TOK];    // sm_[i]: the maximum after token i of the chunk
+    __shared__ float m_start;                     // the maximum before the chunk's first token
     const int e = e0 + blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int q0 = qstart[e], n = qstart[e + 1] - q0;
     if (n <= 0) return;
-    if (tid == 0) sm_[0] = mstate[(size_t)read_slots[e] * slot_stride + h];
+    if (tid == 0) m_start = mstate[(size_t)read_slots[e] * slot_stride + h];
     for (int t0 = 0; t0 < n; t0 += SG_TOK) {
         const int nt = min(SG_TOK, n - t0);
         float il = 0.f, fl = 0.f;
@@ -816,26 +817,34 @@ __global__ void __launch_bounds__(SG_TOK) stabilized_gates_kernel(const float* z
             si[tid] = il, sf[tid] = fl;
         }
         __syncthreads();
-        if (tid == 0) {
-            float m = sm_[0];
-            for (int i = 0; i < nt; ++i) {
+        if (tid == 0) {                           // four tokens a turn, 16 bytes a load and a store: the chain itself is an add and a max a token
+            float m = m_start;
+            int i = 0;
+            for (; i + 4 <= nt; i += 4) {
+                const float4 f4 = *reinterpret_cast<const float4*>(sf + i), i4 = *reinterpret_cast<const float4*>(si + i);
+                float4 o;
+                o.x = fmaxf(f4.x + m, i4.x), o.y = fmaxf(f4.y + o.x, i4.y), o.z = fmaxf(f4.z + o.y, i4.z), o.w = fmaxf(f4.w + o.z, i4.w);
+                *reinterpret_cast<float4*>(sm_ + i) = o;
+                m = o.w;
+            }
+            for (; i < nt; ++i) {
                 m = fmaxf(sf[i] + m, si[i]);
-                sm_[i + 1] = m;
+                sm_[i] = m;
             }
         }
         __syncthreads();
         if (tid < nt) {
             const size_t o = (size_t)(q0 + t0 + tid) * H + h;
-            const float mp = sm_[tid], m = sm_[tid + 1];
+            const float mp = tid == 0 ? m_start : sm_[tid - 1], m = sm_[tid];
             decay[o] = expf(fl + mp - m);
             inw[o] = expf(il - m);
             floor_[o] = expf(-m);
         }
         __syncthreads();
-        if (tid == 0) sm_[0] = sm_[nt];
+        if (tid == 0) m_start = sm_[nt - 1];
     }
     __syncthreads();
-    if (tid == 0) mstate[(size_t)write_slots[e] * slot_stride + h] = sm_[0];
+    if (tid == 0) mstate[(size_t)write_slots[e] * slot_stride + h] = m_start;
 }
 
 IL_EXPORT int il_stabilized_gates(const float* z, int ldz, int i_off, int f_off, float cap, float* mstate, int slot_stride, const int* read_slots,

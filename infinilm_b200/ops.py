@@ -206,8 +206,8 @@ def attention_plain(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, b
                     sink: Optional[torch.Tensor] = None, dist_bias: Optional[torch.Tensor] = None) -> None:
     """Causal attention of every token of `qkv` over its request's cache pages (plain kernel). `qkv` needs the query
     heads only (keys and values are read from the cache). `sink`: float32 [heads], a score per head that joins the
-    softmax's denominator without a value. `dist_bias`: float32 [heads, far + 1], added to the scaled score of a key n
-    positions back as dist_bias[head, min(n, far)]."""
+    softmax's denominator without a value. `dist_bias`: float32 [far + 1, heads], added to the scaled score of a key n
+    positions back as dist_bias[min(n, far), head]."""
     _need_cuda(qkv, out, cache, block_table, tok_pos, tok_entry, sink, dist_bias)
     _check_sink(sink, n_heads)
     _check_dist_bias(dist_bias, n_heads)
@@ -222,7 +222,7 @@ def attention_plain(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, b
                                             _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p])
     _check(f(_ptr(qkv), kind_of(qkv.dtype), qkv.shape[1], _ptr(out), _ptr(cache), _ptr(block_table),
              block_table.shape[1], _ptr(tok_pos), _ptr(tok_entry), page_size, T, n_heads, n_kv_heads, head_dim,
-             scale, int(window or 0), _ptr(sink), _ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[1] - 1, _stream()),
+             scale, int(window or 0), _ptr(sink), _ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[0] - 1, _stream()),
            "attention_plain")
 
 
@@ -232,9 +232,9 @@ def _check_sink(sink: Optional[torch.Tensor], n_heads: int) -> None:
 
 
 def _check_dist_bias(dist_bias: Optional[torch.Tensor], n_heads: int) -> None:
-    if dist_bias is not None and (dist_bias.dtype != torch.float32 or dist_bias.dim() != 2 or dist_bias.shape[0] != n_heads
-                                  or dist_bias.shape[1] < 1 or not dist_bias.is_contiguous()):
-        raise KernelError("attention: the distance bias must be a contiguous float32 [heads, far + 1] tensor")
+    if dist_bias is not None and (dist_bias.dtype != torch.float32 or dist_bias.dim() != 2 or dist_bias.shape[1] != n_heads
+                                  or dist_bias.shape[0] < 1 or not dist_bias.is_contiguous()):
+        raise KernelError("attention: the distance bias must be a contiguous float32 [far + 1, heads] tensor")
 
 
 def norm_add(resid: torch.Tensor, branch: torch.Tensor, weight: torch.Tensor, eps: float, scale: float,
@@ -374,7 +374,7 @@ def attention_decode(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, 
     Scratch: o_part float32 [n_decode*heads*n_splits*head_dim], ml_part float32 [n_decode*heads*n_splits*2]."""
     _need_cuda(qkv, out, cache, block_table, entry_kvlen, o_part, ml_part, sink, dist_bias)
     _check_sink(sink, n_heads)
-    _check_dist_bias(dist_bias, n_heads)      # float32 [heads, far + 1]: added to the scaled score of a key n positions back
+    _check_dist_bias(dist_bias, n_heads)      # float32 [far + 1, heads]: added to the scaled score of a key n positions back
     if qkv.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16:
         raise KernelError("attention_decode: bfloat16 tensors")
     if o_part is None or ml_part is None or o_part.dtype != torch.float32 or ml_part.dtype != torch.float32:
@@ -396,7 +396,7 @@ def attention_decode(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, 
     _check(f(_ptr(qkv), qkv.shape[1], _ptr(out), _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(entry_kvlen),
              page_size, n_decode, n_heads, n_kv_heads, head_dim, scale, int(window or 0), pages_per_split, n_splits,
              _ptr(o_part), _ptr(ml_part), _ptr(kv_map), _ptr(stream_status(qkv.device)) if kv_map is not None else _c_void_p(0),
-             _ptr(sink), 1 if v_is_k else 0, _ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[1] - 1, _stream()), "attention_decode")
+             _ptr(sink), 1 if v_is_k else 0, _ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[0] - 1, _stream()), "attention_decode")
     if n_splits > 1:
         count_launches(1)                         # the merge kernel (a single split needs none: the attention kernel finishes the rows)
 
@@ -458,7 +458,7 @@ def attention_prefill(qkv: torch.Tensor, out: torch.Tensor, cache: torch.Tensor,
                                                 _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p], defines={"HEAD_DIM": head_dim})
     _check(f(_ptr(qkv), qkv.shape[1], _ptr(out), _ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(entry_qstart),
              _ptr(entry_kvlen), page_size, first_entry, n_entries, n_tiles_total, n_heads, n_kv_heads, head_dim, scale,
-             int(window or 0), _ptr(sink), _ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[1] - 1, _stream()), "attention_prefill")
+             int(window or 0), _ptr(sink), _ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[0] - 1, _stream()), "attention_prefill")
 
 
 _tc5_prefill_rows = {}
@@ -514,7 +514,7 @@ def attention_prefill_tc5(qkv: torch.Tensor, out: torch.Tensor, kv_map: torch.Te
              _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p], defines={"HEAD_DIM": head_dim})
     _check(f(_ptr(qkv), qkv.shape[1], _ptr(out), _c_void_p(kv_map.data_ptr() + 256), _ptr(block_table), block_table.shape[1],
              _ptr(entry_qstart), _ptr(entry_kvlen), page_size, first_entry, n_entries, n_tiles_total, n_heads, n_kv_heads,
-             head_dim, scale, int(window or 0), _ptr(stream_status(qkv.device)), _ptr(sink), _ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[1] - 1,
+             head_dim, scale, int(window or 0), _ptr(stream_status(qkv.device)), _ptr(sink), _ptr(dist_bias), 0 if dist_bias is None else dist_bias.shape[0] - 1,
              _stream()), "attention_prefill_tc5")
 
 

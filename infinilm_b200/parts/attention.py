@@ -27,8 +27,8 @@ class PagedAttend:
     `sink`: float32 [heads] on the device or None - a score per head that joins the softmax's denominator without a value.
     `shared_kv`: the mixer writes the same vector to the K and the V plane (one latent that is key and value); the decode
     kernel then reads the K plane alone. The prompt kernels, bound by arithmetic, read both planes as they lie.
-    `dist_bias`: float32 [heads, far + 1] on the device or None - a bias by distance, added to the scaled score of a key n
-    positions back as dist_bias[head, min(n, far)] (constant from `far` on)."""
+    `dist_bias`: float32 [far + 1, heads] on the device or None - a bias by distance, added to the scaled score of a key n
+    positions back as dist_bias[min(n, far), head] (constant from `far` on)."""
 
     # The fast bfloat16 kernels take kernel pages of 16 keys (the cache manager lays larger pages out as runs of them)
     # and at most 64 query heads per kv head; anything else, and the whole float32 path, runs the plain kernel.

@@ -14,7 +14,7 @@ out at hd = max of the two rounded up to 16, the surplus columns zero, as `conv_
 The bias: table [rows, heads]; distances below rows/2 have a row each, the others share the remaining rows on a logarithmic
 scale that reaches the last row at distance `far`: bucket(n) = n for n < rows/2, else
 min(rows - 1, rows/2 + floor(ln(n / (rows/2)) / ln(far / (rows/2)) * (rows - rows/2))). At load it is unrolled into a float32
-table [heads, far + 1] by distance, constant from `far` on, which is what the attention kernels index.
+table [far + 1, heads] by distance, constant from `far` on, which is what the attention kernels index.
 Tensors (under the part's prefix): q, k, v, g, o [out, in]; q.b, k.b, v.b; q.norm, k.norm [dim]; rel [rows, heads].
 """
 from __future__ import annotations
@@ -133,7 +133,7 @@ class QKNormAttention(Mixer):
         self.w_k = t["k.norm"].to(torch.float32).contiguous() if self.own_kv else None
         if self.has_bias:
             idx = torch.tensor(distance_buckets(int(t["rel"].shape[0]), self.bias_far), dtype=torch.long, device=dev)
-            self.core.dist_bias = t["rel"].to(torch.float32)[idx].t().contiguous()      # [heads, far + 1]
+            self.core.dist_bias = t["rel"].to(torch.float32)[idx].contiguous()          # [far + 1, heads]
         if self.sink_zero:
             self.core.sink = torch.zeros(self.nh, dtype=torch.float32, device=dev)
 

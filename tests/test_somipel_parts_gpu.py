@@ -166,7 +166,7 @@ def _run_attention(kernel, c, nh, nkv, hd, scale, table, far, dtype, sink, split
     cache, bt = c["cache"].to(dt).cuda(), c["bt"].cuda()
     db = None
     if table is not None:
-        db = table[torch.tensor(distance_buckets(table.shape[0], far))].t().contiguous().float().cuda()      # [heads, far + 1]
+        db = table[torch.tensor(distance_buckets(table.shape[0], far))].contiguous().float().cuda()      # [far + 1, heads]
     sk = torch.zeros(nh, device="cuda") if sink else None
     T = q.shape[0]
     out = torch.full((T, nh * hd), float("nan"), device="cuda", dtype=dt)
