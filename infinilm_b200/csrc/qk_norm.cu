@@ -10,7 +10,29 @@
 // Cache layout of one layer: [page][0=K,1=V][kv head][slot in page][hd]. One warp per (token, head).
 #include "common.cuh"
 
-template <typename TA>
+// four neighbouring values at a time (16 bytes of f32, 8 of bfloat16)
+__device__ __forceinline__ float4 qn_ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 qn_ld4(const __nv_bfloat16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x), b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+__device__ __forceinline__ void qn_st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void qn_st4(__nv_bfloat16* p, float4 v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<const uint32_t*>(&a);
+    u.y = *reinterpret_cast<const uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+__device__ __forceinline__ float4 qn_w4(const void* w, int kind, int d) {
+    return make_float4(il_load_any(w, kind, d), il_load_any(w, kind, d + 1), il_load_any(w, kind, d + 2), il_load_any(w, kind, d + 3));
+}
+
+// The form for sizes and offsets that are multiples of 4 (rows, segments and heads then start on 8- or 16-byte borders): the
+// lanes hold 4 neighbouring columns instead of every 32nd (the sum of squares is gathered in another order). VEC 1 is the form for
+// every size.
+template <typename TA, int VEC>
 __global__ void qk_norm_store_kernel(const TA* proj, int ld, int q_off, int k_off, int v_off, int nh, int nkv, int dk, int dv, int hd,
                                      const void* __restrict__ wq, const void* __restrict__ wk, int w_kind, float eps, float t_coef,
                                      int t_every, TA* __restrict__ q_out, const int* __restrict__ tok_pos,
@@ -26,16 +48,35 @@ __global__ void qk_norm_store_kernel(const TA* proj, int ld, int q_off, int k_of
     const TA* row = proj + (size_t)t * ld;
     if (j < nh) {                                 // a query head
         const TA* x = row + q_off + (size_t)j * dk;
+        TA* o = q_out + ((size_t)t * nh + j) * hd;
         float ss = 0.f;
-        for (int d = lane; d < dk; d += 32) {
-            const float a = il_to_f(x[d]);
-            ss += a * a;
+        if (VEC == 4) {
+            for (int d = 4 * lane; d < dk; d += 128) {
+                const float4 a = qn_ld4(x + d);
+                ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+            }
+        } else {
+            for (int d = lane; d < dk; d += 32) {
+                const float a = il_to_f(x[d]);
+                ss += a * a;
+            }
         }
         ss = il_warp_sum(ss);
         float r = 1.f / sqrtf(ss / (float)dk + eps);
         if (t_every > 0) r *= 1.f + t_coef * logf((float)((pos + 1) / t_every) + 1.f);
-        TA* o = q_out + ((size_t)t * nh + j) * hd;
-        for (int d = lane; d < hd; d += 32) o[d] = il_from_f<TA>(d < dk ? il_to_f(x[d]) * r * il_load_any(wq, w_kind, d) : 0.f);
+        if (VEC == 4) {
+            for (int d = 4 * lane; d < hd; d += 128) {
+                float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (d < dk) {
+                    const float4 w = qn_w4(wq, w_kind, d);
+                    a = qn_ld4(x + d);
+                    a.x *= r * w.x, a.y *= r * w.y, a.z *= r * w.z, a.w *= r * w.w;
+                }
+                qn_st4(o + d, a);
+            }
+        } else {
+            for (int d = lane; d < hd; d += 32) o[d] = il_from_f<TA>(d < dk ? il_to_f(x[d]) * r * il_load_any(wq, w_kind, d) : 0.f);
+        }
         return;
     }
     if (!cache) return;
@@ -47,16 +88,39 @@ __global__ void qk_norm_store_kernel(const TA* proj, int ld, int q_off, int k_of
     if (is_k) {
         const TA* x = row + k_off + (size_t)g * dk;
         float ss = 0.f;
-        for (int d = lane; d < dk; d += 32) {
-            const float a = il_to_f(x[d]);
-            ss += a * a;
+        if (VEC == 4) {
+            for (int d = 4 * lane; d < dk; d += 128) {
+                const float4 a = qn_ld4(x + d);
+                ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+            }
+        } else {
+            for (int d = lane; d < dk; d += 32) {
+                const float a = il_to_f(x[d]);
+                ss += a * a;
+            }
         }
         ss = il_warp_sum(ss);
         const float r = 1.f / sqrtf(ss / (float)dk + eps);
-        for (int d = lane; d < hd; d += 32) dst[d] = il_from_f<TA>(d < dk ? il_to_f(x[d]) * r * il_load_any(wk, w_kind, d) : 0.f);
+        if (VEC == 4) {
+            for (int d = 4 * lane; d < hd; d += 128) {
+                float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (d < dk) {
+                    const float4 w = qn_w4(wk, w_kind, d);
+                    a = qn_ld4(x + d);
+                    a.x *= r * w.x, a.y *= r * w.y, a.z *= r * w.z, a.w *= r * w.w;
+                }
+                qn_st4(dst + d, a);
+            }
+        } else {
+            for (int d = lane; d < hd; d += 32) dst[d] = il_from_f<TA>(d < dk ? il_to_f(x[d]) * r * il_load_any(wk, w_kind, d) : 0.f);
+        }
     } else {
         const TA* x = row + v_off + (size_t)g * dv;
-        for (int d = lane; d < hd; d += 32) dst[d] = d < dv ? x[d] : il_from_f<TA>(0.f);
+        if (VEC == 4) {
+            for (int d = 4 * lane; d < hd; d += 128) qn_st4(dst + d, d < dv ? qn_ld4(x + d) : make_float4(0.f, 0.f, 0.f, 0.f));
+        } else {
+            for (int d = lane; d < hd; d += 32) dst[d] = d < dv ? x[d] : il_from_f<TA>(0.f);
+        }
     }
 }
 
@@ -69,15 +133,18 @@ IL_EXPORT int il_qk_norm_store(const void* proj, int act_kind, int ld, int q_off
     const long long warps = (long long)T * (nh + (k_off >= 0 ? 2 * nkv : 0));
     const long long blocks = (warps + 3) / 4;
     if (blocks > 0x7fffffffLL) return IL_UNSUPPORTED;
-    if (act_kind == IL_F32)
-        IL_LAUNCH(qk_norm_store_kernel<float>, (int)blocks, 128, 0, stream, (const float*)proj, ld, q_off, k_off, v_off, nh, nkv, dk, dv, hd, wq,
-                  wk, w_kind, eps, t_coef, t_every, (float*)q_out, tok_pos, tok_entry, block_table, bt_stride, (float*)cache, page_size, T);
-    else if (act_kind == IL_BF16)
-        IL_LAUNCH(qk_norm_store_kernel<__nv_bfloat16>, (int)blocks, 128, 0, stream, (const __nv_bfloat16*)proj, ld, q_off, k_off, v_off, nh, nkv,
-                  dk, dv, hd, wq, wk, w_kind, eps, t_coef, t_every, (__nv_bfloat16*)q_out, tok_pos, tok_entry, block_table, bt_stride,
-                  (__nv_bfloat16*)cache, page_size, T);
-    else
-        return IL_BAD_ARG;
+    if (act_kind != IL_F32 && act_kind != IL_BF16) return IL_BAD_ARG;
+    const bool vec = ((ld | q_off | v_off | dk | dv | hd) & 3) == 0 && (k_off < 0 || (k_off & 3) == 0) &&
+                     (((uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)cache) & 15) == 0;
+#define QN_GO(TA, VEC)                                                                                                                  \
+    IL_LAUNCH((qk_norm_store_kernel<TA, VEC>), (int)blocks, 128, 0, stream, (const TA*)proj, ld, q_off, k_off, v_off, nh, nkv, dk, dv, hd, wq, wk, \
+              w_kind, eps, t_coef, t_every, (TA*)q_out, tok_pos, tok_entry, block_table, bt_stride, (TA*)cache, page_size, T)
+    if (act_kind == IL_F32) {
+        if (vec) QN_GO(float, 4); else QN_GO(float, 1);
+    } else {
+        if (vec) QN_GO(__nv_bfloat16, 4); else QN_GO(__nv_bfloat16, 1);
+    }
+#undef QN_GO
     IL_LAUNCH_CHECK();
     return IL_OK;
 }
@@ -98,10 +165,39 @@ __global__ void gate_pack_kernel(const TA* y, int hd, const TA* gate, int ldg, i
     }
 }
 
+template <typename TA>
+__global__ void gate_pack4_kernel(const TA* y, int hd, const TA* gate, int ldg, int g_off, TA* __restrict__ out, int nh, int dv, int T) {
+    il_pdl_wait();
+    const int n4 = (nh * dv) >> 2;
+    const long long total = (long long)T * n4;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / n4;
+        const int jc = (int)(i - t * n4) << 2, h = jc / dv, c = jc - h * dv;
+        float4 v = qn_ld4(y + ((size_t)t * nh + h) * hd + c);
+        if (gate) {
+            const float4 z = qn_ld4(gate + (size_t)t * ldg + g_off + jc);
+            v.x = v.x / (1.f + expf(-z.x)), v.y = v.y / (1.f + expf(-z.y)), v.z = v.z / (1.f + expf(-z.z)), v.w = v.w / (1.f + expf(-z.w));
+        }
+        qn_st4(out + (size_t)t * nh * dv + jc, v);
+    }
+}
+
 IL_EXPORT int il_gate_pack(const void* y, int act_kind, int hd, const void* gate, int ldg, int g_off, void* out, int nh, int dv, int T,
                            cudaStream_t stream) {
     if (T <= 0) return IL_OK;
     if (nh <= 0 || dv <= 0 || dv > hd) return IL_BAD_ARG;
+    if (act_kind != IL_F32 && act_kind != IL_BF16) return IL_BAD_ARG;
+    if (((hd | dv | ldg | g_off) & 3) == 0 && (((uintptr_t)y | (uintptr_t)gate | (uintptr_t)out) & 15) == 0) {
+        const long long g4 = ((long long)T * nh * dv / 4 + 255) / 256;
+        const int blocks4 = (int)(g4 > 148 * 16 ? 148 * 16 : g4);
+        if (act_kind == IL_F32)
+            IL_LAUNCH(gate_pack4_kernel<float>, blocks4, 256, 0, stream, (const float*)y, hd, (const float*)gate, ldg, g_off, (float*)out, nh, dv, T);
+        else
+            IL_LAUNCH(gate_pack4_kernel<__nv_bfloat16>, blocks4, 256, 0, stream, (const __nv_bfloat16*)y, hd, (const __nv_bfloat16*)gate, ldg,
+                      g_off, (__nv_bfloat16*)out, nh, dv, T);
+        IL_LAUNCH_CHECK();
+        return IL_OK;
+    }
     const long long g = ((long long)T * nh * dv + 255) / 256;
     const int blocks = (int)(g > 148 * 16 ? 148 * 16 : g);
     if (act_kind == IL_F32)

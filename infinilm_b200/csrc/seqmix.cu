@@ -790,11 +790,13 @@ IL_EXPORT int il_group_norm_gate_den(const float* x, int ldx, const void* w, int
 //   i_t = cap tanh(zi_t / cap),  f_t = logsigmoid(cap tanh(zf_t / cap))          (cap <= 0: zi, logsigmoid(zf) as they are)
 //   m_t = max(f_t + m_(t-1), i_t);  decay_t = exp(f_t + m_(t-1) - m_t);  inw_t = exp(i_t - m_t);  floor_t = exp(-m_t)
 // m is part of the request's state (float32 [slots, heads]; the zero slot gives m = 0). zi, zf: float32 columns of z, one per
-// head. One block per (entry, head): the transcendental parts are done by all threads for 128 tokens at a time, the chain
+// head. One block per (entry, head): the transcendental parts are done by all threads for a chunk of tokens at a time, the chain
 // of maxima by one thread in the order of the sequence (an add and a max a token), so a token's gates do not depend on
 // how the sequence was cut into steps.
-#define SG_TOK 128
+// (SG_TOK tokens at a time: 512 where the entries bring long portions - the loads' and the exponentials' latency is paid once a
+// chunk -, 128 where they bring few tokens.)
 __device__ __forceinline__ float sm_logsigmoid(float x) { return x >= 0.f ? -log1pf(expf(-x)) : x - log1pf(expf(x)); }
+template <int SG_TOK>
 __global__ void __launch_bounds__(SG_TOK) stabilized_gates_kernel(const float* z, int ldz, int i_off, int f_off, float cap, float* mstate,
                                                                   int slot_stride, const int* __restrict__ read_slots,
                                                                   const int* __restrict__ write_slots, const int* __restrict__ qstart,
@@ -849,11 +851,15 @@ __global__ void __launch_bounds__(SG_TOK) stabilized_gates_kernel(const float* z
 
 IL_EXPORT int il_stabilized_gates(const float* z, int ldz, int i_off, int f_off, float cap, float* mstate, int slot_stride, const int* read_slots,
                                   const int* write_slots, const int* qstart, float* decay, float* inw, float* floor_, int H, int E, int e0,
-                                  cudaStream_t stream) {
+                                  int T, cudaStream_t stream) {
     if (E <= 0) return IL_OK;
     if (H <= 0 || e0 < 0 || slot_stride < H) return IL_BAD_ARG;
-    stabilized_gates_kernel<<<dim3(E, H), SG_TOK, 0, stream>>>(z, ldz, i_off, f_off, cap, mstate, slot_stride, read_slots, write_slots, qstart,
-                                                                decay, inw, floor_, H, e0);
+    if (T >= 256 * E)                             // (T: the rows of the step; only their average per entry is used)
+        stabilized_gates_kernel<512><<<dim3(E, H), 512, 0, stream>>>(z, ldz, i_off, f_off, cap, mstate, slot_stride, read_slots, write_slots,
+                                                                     qstart, decay, inw, floor_, H, e0);
+    else
+        stabilized_gates_kernel<128><<<dim3(E, H), 128, 0, stream>>>(z, ldz, i_off, f_off, cap, mstate, slot_stride, read_slots, write_slots,
+                                                                     qstart, decay, inw, floor_, H, e0);
     IL_LAUNCH_CHECK();
     return IL_OK;
 }

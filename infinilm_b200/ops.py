@@ -1231,9 +1231,9 @@ def stabilized_gates(z: torch.Tensor, i_off: int, f_off: int, cap: float, m_stat
         if t.dtype != torch.float32 or tuple(t.shape) != (T, n_heads) or not t.is_contiguous():
             raise KernelError("stabilized_gates: outputs float32 [T, heads]")
     f = _fn("seqmix", "il_stabilized_gates", [_c_void_p, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
-                                              _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p])
+                                              _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p])
     _check(f(_ptr(z), z.stride(0), i_off, f_off, cap, _ptr(m_state), m_state.stride(0), _ptr(read_slots), _ptr(write_slots),
-             _ptr(entry_qstart), _ptr(decay), _ptr(in_weight), _ptr(den_floor), n_heads, n_entries, first_entry, _stream()),
+             _ptr(entry_qstart), _ptr(decay), _ptr(in_weight), _ptr(den_floor), n_heads, n_entries, first_entry, T, _stream()),
            "stabilized_gates")
 
 

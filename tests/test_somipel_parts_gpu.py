@@ -54,8 +54,10 @@ def test_norm_on_the_branch_then_add(cuda_device, dtype, T, H):
 # ---- query and key norms, temperature, cache write -----------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("nh,nkv,dk,dv,v_from_k,temp", [(4, 2, 32, 64, False, None), (3, 1, 24, 24, True, (0.7, 5)), (2, 2, 128, 128, False, (0.5, 1)),
-                                                         (6, 3, 20, 12, False, None), (5, 5, 40, 40, True, (1.5, 16))])
-def test_qk_norm_temperature_and_store(cuda_device, dtype, nh, nkv, dk, dv, v_from_k, temp):
+                                                         (6, 3, 20, 12, False, None), (5, 5, 40, 40, True, (1.5, 16)), (2, 1, 18, 7, False, (0.3, 2)),
+                                                         (1, 1, 256, 132, False, None)])
+@pytest.mark.parametrize("lead,tail", [(3, 5), (4, 8)])      # segments on and off 16-byte borders: both forms of the kernel
+def test_qk_norm_temperature_and_store(cuda_device, dtype, nh, nkv, dk, dv, v_from_k, temp, lead, tail):
     from infinilm_b200 import ops
     torch.manual_seed(nh * dk)
     dt = DT[dtype]
@@ -65,8 +67,8 @@ def test_qk_norm_temperature_and_store(cuda_device, dtype, nh, nkv, dk, dv, v_fr
     bt = _i32([[5, 2, 7], [3, -1, -1]])
     T = len(pos)
     nq, nk, nv = nh * dk, nkv * dk, (0 if v_from_k else nkv * dv)
-    proj = (torch.randn(T, 3 + nq + nk + nv + 5) * 2.0).to(dt)
-    q_off, k_off = 3, 3 + nq
+    proj = (torch.randn(T, lead + nq + nk + nv + tail) * 2.0).to(dt)
+    q_off, k_off = lead, lead + nq
     v_off = k_off if v_from_k else k_off + nk
     wq, wk = 1.0 + 0.2 * torch.randn(dk), 1.0 + 0.2 * torch.randn(dk)
     cache = torch.full((9, 2, nkv, 16, hd), 9.0, dtype=dt, device="cuda")
@@ -107,14 +109,14 @@ def test_gate_per_column_with_packing(cuda_device, dtype):
     from infinilm_b200 import ops
     torch.manual_seed(3)
     dt = DT[dtype]
-    T, nh, hd, dv = 37, 3, 32, 20
-    y, gate = torch.randn(T, nh * hd).to(dt), (torch.randn(T, 7 + nh * dv) * 3).to(dt)
-    out = torch.empty(T, nh * dv, dtype=dt, device="cuda")
-    ops.gate_pack(y.cuda(), hd, gate.cuda(), 7, out, nh, dv)
-    want = y.double().view(T, nh, hd)[:, :, :dv].reshape(T, -1) * torch.sigmoid(gate.double()[:, 7:])
-    _close(out, want, dtype, "gate_pack")
-    ops.gate_pack(y.cuda(), hd, None, 0, out, nh, dv)
-    assert torch.equal(out.cpu(), y.view(T, nh, hd)[:, :, :dv].reshape(T, -1))
+    for T, nh, hd, dv, lead in ((37, 3, 32, 20, 7), (37, 3, 32, 20, 8), (5, 2, 128, 128, 0), (9, 4, 16, 13, 4), (3000, 16, 64, 64, 64)):
+        y, gate = torch.randn(T, nh * hd).to(dt), (torch.randn(T, lead + nh * dv + (-(lead + nh * dv)) % 4) * 3).to(dt)
+        out = torch.empty(T, nh * dv, dtype=dt, device="cuda")
+        ops.gate_pack(y.cuda(), hd, gate.cuda(), lead, out, nh, dv)
+        want = y.double().view(T, nh, hd)[:, :, :dv].reshape(T, -1) * torch.sigmoid(gate.double()[:, lead:lead + nh * dv])
+        _close(out, want, dtype, f"gate_pack {T, nh, hd, dv, lead}")
+        ops.gate_pack(y.cuda(), hd, None, 0, out, nh, dv)
+        assert torch.equal(out.cpu(), y.view(T, nh, hd)[:, :, :dv].reshape(T, -1))
 
 
 # ---- the bias by distance in the four attention kernels ---------------------------------------------------------------------
@@ -267,7 +269,7 @@ def _gate_inputs(T, H, seed):
 @pytest.mark.parametrize("H", [1, 3, 8])
 def test_log_space_gates_and_running_maximum_in_portions(cuda_device, H, cap):
     from infinilm_b200 import ops
-    T = 300
+    T = 1100                                      # (beyond two chunks of the kernel's form for long portions, and of its other form)
     z = _gate_inputs(T, H, H)
     zi, zf = z[:, 1:1 + H].double(), z[:, 1 + H:1 + 2 * H].double()
     il = P.capped(zi, cap) if cap > 0 else zi
@@ -279,7 +281,7 @@ def test_log_space_gates_and_running_maximum_in_portions(cuda_device, H, cap):
         want.append(torch.stack([torch.exp(fl[t] + m - mn), torch.exp(il[t] - mn), torch.exp(-mn)]))
         m = mn
     want = torch.stack(want)                      # [T, 3, H]
-    for cuts in ([T], [129, 1, 1, 2, 127, 40], [1] * 20 + [280]):
+    for cuts in ([T], [129, 1, 1, 2, 127, 40, 800], [1] * 20 + [280, 800], [511, 513, 76], [200, 255, 257, 388]):
         mstate = torch.zeros(4, H, device="cuda")
         mstate[2] = 5.0                           # a slot that an earlier request left dirty: the first step reads slot 0
         outs, a = [], 0
