@@ -303,7 +303,7 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
             for (int j = 0; j < 4; ++j) {
                 const int key = key0 + nt * 8 + (j & 1);
                 float v = s[nt][j] * scale_log2;
-                if (dist_bias) v += db_near ? db_row[j >> 1][(size_t)max(0, min(kvlen - 1 - key, dist_far)) * nh] * 1.4426950408889634f : db_far[j >> 1];
+                if (dist_bias) v += db_near ? db_row[j >> 1][max(0, min(kvlen - 1 - key, dist_far)) * nh] * 1.4426950408889634f : db_far[j >> 1];
                 s[nt][j] = (key >= lo && key < hi) ? v : -INFINITY;
             }
 #pragma unroll
@@ -583,7 +583,7 @@ IL_EXPORT int il_attn_decode(const void* qkv, int row_stride, void* out, const v
                              const void* kv_map, int* status, const float* sink, int v_is_k, const float* dist_bias, int dist_far,
                              cudaStream_t stream) {
     if (n_decode <= 0) return IL_OK;
-    if (dist_bias && dist_far < 0) return IL_BAD_ARG;
+    if (dist_bias && (dist_far < 0 || (long long)(dist_far + 1) * nh > 0x7fffffffLL)) return IL_BAD_ARG;
     if (hd != HEAD_DIM || page_size != AD_PAGE) return IL_UNSUPPORTED;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || pages_per_split < 0 || n_splits <= 0) return IL_BAD_ARG;
     if (n_splits > AD_MAX_SPLITS) return IL_UNSUPPORTED;

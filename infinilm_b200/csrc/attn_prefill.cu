@@ -183,7 +183,7 @@ __global__ void __launch_bounds__(AP_WARPS * 32) attn_prefill_kernel(
                 for (int j = 0; j < 4; ++j) {
                     const int h = j >> 1;
                     const int key = k0 + nt * 8 + (lane & 3) * 2 + (j & 1);
-                    if (dist_bias) s[p][nt][j] += db_near ? db_row[h][(size_t)max(0, min(rpos[h] - key, dist_far)) * nh] * inv_scale : db_far[h];
+                    if (dist_bias) s[p][nt][j] += db_near ? db_row[h][max(0, min(rpos[h] - key, dist_far)) * nh] * inv_scale : db_far[h];
                     if (need_mask) {
                         if (!(key <= rpos[h] && key >= rlo[h])) s[p][nt][j] = -INFINITY;
                     }
@@ -254,7 +254,7 @@ IL_EXPORT int il_attn_prefill(const void* qkv, int row_stride, void* out, const 
                               int first_entry, int n_entries, int n_tiles_total, int nh, int nkv, int hd, float scale,
                               int window, const float* sink, const float* dist_bias, int dist_far, cudaStream_t stream) {
     if (n_tiles_total <= 0 || first_entry >= n_entries) return IL_OK;
-    if (dist_bias && (dist_far < 0 || !(scale > 0.f))) return IL_BAD_ARG;
+    if (dist_bias && (dist_far < 0 || !(scale > 0.f) || (long long)(dist_far + 1) * nh > 0x7fffffffLL)) return IL_BAD_ARG;
     if (hd != HEAD_DIM || page_size != AP_PAGE) return IL_UNSUPPORTED;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0) return IL_BAD_ARG;
     const int G = nh / nkv;

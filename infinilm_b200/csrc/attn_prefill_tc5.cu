@@ -297,13 +297,13 @@ __global__ void __launch_bounds__(PT_THREADS, PT_BLOCKS_PER_SM) attn_prefill_tc5
 #pragma unroll
                     for (int c = 0; c < PT_KEYS; ++c) sv[c] = __float_as_uint(__uint_as_float(sv[c]) + db_far);
                 } else if (rpos - kb <= dist_far && rpos - kb >= PT_KEYS - 1) {      // every key of the tile has a line of its own
-                    const float* dbp = db_row + (size_t)(rpos - kb) * nh;
+                    const int at = (rpos - kb) * nh;          // (32-bit index arithmetic: the table has far fewer than 2^31 entries)
 #pragma unroll
-                    for (int c = 0; c < PT_KEYS; ++c) sv[c] = __float_as_uint(fmaf(dbp[-(ptrdiff_t)c * nh], inv_scale, __uint_as_float(sv[c])));
+                    for (int c = 0; c < PT_KEYS; ++c) sv[c] = __float_as_uint(fmaf(db_row[at - c * nh], inv_scale, __uint_as_float(sv[c])));
                 } else {
 #pragma unroll
                     for (int c = 0; c < PT_KEYS; ++c)
-                        sv[c] = __float_as_uint(fmaf(db_row[(size_t)max(0, min(rpos - kb - c, dist_far)) * nh], inv_scale, __uint_as_float(sv[c])));
+                        sv[c] = __float_as_uint(fmaf(db_row[max(0, min(rpos - kb - c, dist_far)) * nh], inv_scale, __uint_as_float(sv[c])));
                 }
             }
             if (kb + PT_KEYS - 1 > rpos || kb < rlo) {        // the tile touches this row's causal or window edge
@@ -420,7 +420,7 @@ IL_EXPORT int il_attn_prefill_tc5(const void* qkv, int row_stride, void* out, co
                                   int n_entries, int n_tiles_total, int nh, int nkv, int hd, float scale, int window, int* status,
                                   const float* sink, const float* dist_bias, int dist_far, cudaStream_t stream) {
     if (n_tiles_total <= 0 || first_entry >= n_entries) return IL_OK;
-    if (dist_bias && dist_far < 0) return IL_BAD_ARG;
+    if (dist_bias && (dist_far < 0 || (long long)(dist_far + 1) * nh > 0x7fffffffLL)) return IL_BAD_ARG;
     if (hd != HEAD_DIM || page_size != PT_PAGE || !kv_map || !status) return IL_UNSUPPORTED;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0) return IL_BAD_ARG;
     const int G = nh / nkv;

@@ -53,12 +53,27 @@ def _err(got, ref):
     return (got - ref).pow(2).mean(dim=-1).sqrt() / ref.pow(2).mean(dim=-1).sqrt()
 
 
+def one_kind(kind: str) -> dict:
+    """Models of a single kind of layer: nothing but matrix memories (no pages at all), nothing but one kind of attention, and
+    one layer whose keys and values every other layer borrows."""
+    layers = {"mlstm": [_mlstm(2, 16, 24, 15.0, 40), _mlstm(3, 8, 8, 4.0, None)],
+              "attention_2": [_att2(4, 2, 32, 0.2, (0.5, 4), 40), _att2(2, 2, 16, 0.3, None, None)],
+              "attention": [_att(2, 1, 16, 32, 0.25, 8, 30, 40), _att(4, 4, 64, 64, 0.1, 16, 100, None)],
+              "borrowers": [_att(2, 1, 32, 16, 0.2, 6, 50, 40), _att(3, 1, 32, 16, 0.3, 10, 12, None, kv_from=0),
+                            _att(1, 1, 32, 16, 0.1, 4, 70, 24, kv_from=0), _att(4, 1, 32, 16, 0.2, 12, 7, 24, kv_from=0)]}[kind]
+    return {"architecture": "Somipel", "vocab": 97, "width": 64, "norm": {"eps": 1e-5}, "residual_mult": 0.6, "layers": layers}
+
+
+KINDS = ["mlstm", "attention_2", "attention", "borrowers"]
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("seed", list(range(14)))
+@pytest.mark.parametrize("seed", list(range(14)) + KINDS)
 def test_random_configuration(cuda_device, seed, dtype):
     from infinilm_b200.config import config_from_json
     from infinilm_b200.engine import Engine, StepEntry
-    raw = random_config(seed)
+    raw = random_config(seed) if isinstance(seed, int) else one_kind(seed)
+    seed = seed if isinstance(seed, int) else 50 + KINDS.index(seed)
     w = make_weights(raw, seed, peak=3.0 if dtype == "float32" else 2.0)
     ids = token_ids(75, raw["vocab"], seed)
     other = token_ids(30, raw["vocab"], seed + 100)
