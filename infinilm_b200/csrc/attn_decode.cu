@@ -189,7 +189,7 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(
         }
         return;
     }
-    const int lo = (window > 0 && kvlen - window > 0) ? kvlen - window : 0;
+    const int lo = il_mask_lo(kvlen - 1, window);
     const int first_page = lo / AD_PAGE, last_page = (kvlen - 1) / AD_PAGE;
     // pages_per_split 0: this request's pages are divided evenly over the splits
     if (pages_per_split <= 0) pages_per_split = (last_page - first_page + n_splits) / n_splits;
@@ -490,7 +490,7 @@ __global__ void __launch_bounds__(128) attn_decode_merge_kernel(const float* o_p
     // the lengths come with the step's descriptors, not from the kernel before: read them while that one still runs
     const int kvlen = row < n_rows ? entry_kvlen[row / nh] : 1;
     const float sink_log2 = (sink && row < n_rows) ? sink[row % nh] * 1.4426950408889634f : -INFINITY;
-    const int lo = (window > 0 && kvlen - window > 0) ? kvlen - window : 0;
+    const int lo = il_mask_lo(kvlen - 1, window);
     const int n_pages = (kvlen - 1) / AD_PAGE - lo / AD_PAGE + 1;
     if (pages_per_split <= 0) pages_per_split = (n_pages + n_splits - 1) / n_splits;
     int n_valid = (n_pages + pages_per_split - 1) / pages_per_split;

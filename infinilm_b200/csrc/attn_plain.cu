@@ -25,7 +25,7 @@ __global__ void attn_plain_kernel(const TA* __restrict__ qkv, int row_stride, TA
     const int g = j / (nh / nkv);
     const int pos = tok_pos[t];
     const int* bt = block_table + (size_t)tok_entry[t] * bt_stride;
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int lo = il_mask_lo(pos, window);
 
     float q[AP_MAX_PER_LANE], acc[AP_MAX_PER_LANE];
     const TA* qrow = qkv + (size_t)t * row_stride + (size_t)j * hd;

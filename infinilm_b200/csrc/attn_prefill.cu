@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(AP_WARPS * 32) attn_prefill_kernel(
         const int tl = rvalid[h] ? r / G : 0, hh = rvalid[h] ? r - tl * G : 0;
         rpos[h] = start_pos + (tok0 - q0) + tl;
         rhead[h] = g * G + hh;
-        rlo[h] = (window > 0 && rpos[h] - window + 1 > 0) ? rpos[h] - window + 1 : 0;
+        rlo[h] = il_mask_lo(rpos[h], window);
         qptr[h] = rvalid[h] ? qkv + (size_t)(tok0 + tl) * row_stride + (size_t)(g * G + hh) * AT_HD : nullptr;
         optr[h] = rvalid[h] ? out + (size_t)(tok0 + tl) * nh * AT_HD + (size_t)(g * G + hh) * AT_HD : nullptr;
         if (!rvalid[h]) { rpos[h] = -1; rlo[h] = 0; }
@@ -110,7 +110,7 @@ __global__ void __launch_bounds__(AP_WARPS * 32) attn_prefill_kernel(
         wmax_lo = max(wmax_lo, __shfl_xor_sync(0xffffffffu, wmax_lo, off));
     }
     const int bpos_first = start_pos + (tok0 - q0), bpos_last = bpos_first + n_tok - 1;
-    const int blo = (window > 0 && bpos_first - window + 1 > 0) ? bpos_first - window + 1 : 0;
+    const int blo = il_mask_lo(bpos_first, window);
     const int page_first = blo / AP_PAGE, page_last = bpos_last / AP_PAGE;
     const int n_tiles = (page_last - page_first) / AP_TILE_PAGES + 1;
 

@@ -113,7 +113,7 @@ __global__ void __launch_bounds__(PT_THREADS, PT_BLOCKS_PER_SM) attn_prefill_tc5
     const int rows_valid = n_tok * G;
     const int* bt = block_table + (size_t)e * bt_stride;
     const int bpos_first = start_pos + (tok0 - q0), bpos_last = bpos_first + n_tok - 1;
-    const int blo = (window > 0 && bpos_first - window + 1 > 0) ? bpos_first - window + 1 : 0;
+    const int blo = il_mask_lo(bpos_first, window);
     const int page_first = blo / PT_PAGE, page_last = bpos_last / PT_PAGE;
     const int n_tiles = (page_last - page_first) / PT_TILE_PAGES + 1;
 
@@ -257,7 +257,7 @@ __global__ void __launch_bounds__(PT_THREADS, PT_BLOCKS_PER_SM) attn_prefill_tc5
         const bool rvalid = r < rows_valid;
         const int tl = rvalid ? r / G : 0, hh = rvalid ? r - tl * G : 0;
         const int rpos = rvalid ? bpos_first + tl : -1;       // a row that is not there masks every key
-        const int rlo = (rvalid && window > 0 && rpos - window + 1 > 0) ? rpos - window + 1 : 0;
+        const int rlo = rvalid ? il_mask_lo(rpos, window) : 0;
         {   // Q: this row's head_dim values into the swizzled K-major tile (16-byte chunk c of row r at chunk c ^ (r % 8))
             const uint4* src = rvalid ? reinterpret_cast<const uint4*>(qkv + (size_t)(tok0 + tl) * row_stride + (size_t)(g * G + hh) * PT_HD) : nullptr;
 #pragma unroll

@@ -67,6 +67,16 @@ __device__ __forceinline__ float il_block_max(float v, float* sh) {
     return t;
 }
 
+// The lowest position a query at position `pos` sees, for the one integer by which the attention kernels take their mask:
+// window > 0: a sliding window, positions pos - window + 1 .. pos; window < 0: runs ("chunks") of -window positions counted
+// from position 0 of the sequence, a query seeing its own run only, from the run's first position to itself; 0: every
+// position up to pos. It never decreases with pos, so the lowest bound of a tile of consecutive queries is its first query's.
+__device__ __forceinline__ int il_mask_lo(int pos, int window) {
+    if (window > 0) return pos - window + 1 > 0 ? pos - window + 1 : 0;
+    if (window < 0 && pos > 0) return pos - pos % (-window);
+    return 0;
+}
+
 // SiLU(g) * u for the bfloat16 path: exponential and division by the fast units (relative error near 2^-21, far below a
 // bfloat16 step). The decode product's epilogue and the SwiGLU kernel both use it, so a token's activation does not
 // depend on which of the two computed it. The float32 path keeps expf and a true division.

@@ -26,10 +26,52 @@ __device__ __forceinline__ void ld8(const float* p, float (&v)[8]) {
 }
 
 // One warp picks the `top` largest of a token's E logits in shared memory (overwritten), the lower expert winning a
-// tie, and writes the experts and the softmax over the chosen logits alone.
-__device__ __forceinline__ void moe_pick(float* z, int E, int top, int* __restrict__ idx, float* __restrict__ wt, int lane) {
+// tie, and writes the experts and their weights. Two rules:
+//   rule 0: the largest logits are chosen; the weights are the softmax over the chosen logits alone.
+//   rule 1: scores s = softmax of the logits over all E; the largest s + corr are chosen (`corr`: one number per expert, or
+//           null); the weights are the chosen experts' s over their sum (+ 1e-20), times out_scale.
+__device__ __forceinline__ void moe_pick(float* z, int E, int top, int* __restrict__ idx, float* __restrict__ wt, int lane, int rule = 0,
+                                         const void* __restrict__ corr = nullptr, int c_kind = 0, float out_scale = 1.f) {
     float chosen_v[MOE_MAX_TOP];
     float vmax = 0.f, den = 0.f;
+    if (rule == 1) {
+        float mx = -INFINITY;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+        mx = il_warp_max(mx);
+        float sum = 0.f;
+        for (int e = lane; e < E; e += 32) sum += expf(z[e] - mx);
+        sum = il_warp_sum(sum);
+        for (int e = lane; e < E; e += 32) z[e] = expf(z[e] - mx) / sum;      // the scores; a chosen one is marked by -1
+        __syncwarp();
+        for (int k = 0; k < top; ++k) {
+            float bv = -INFINITY;
+            int bi = 0x7fffffff;
+            for (int e = lane; e < E; e += 32) {
+                if (z[e] < 0.f) continue;
+                const float v = z[e] + (corr ? il_load_any(corr, c_kind, e) : 0.f);
+                if (v > bv || (v == bv && e < bi)) bv = v, bi = e;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (ov > bv || (ov == bv && oi < bi)) bv = ov, bi = oi;
+            }
+            if (bi >= E) bi = 0;                  // every score NaN: still a valid expert
+            const float sb = z[bi];
+            chosen_v[k] = sb;
+            den += sb;
+            __syncwarp();
+            if (lane == 0) {
+                idx[k] = bi;
+                z[bi] = -1.f;
+            }
+            __syncwarp();
+        }
+        if (lane == 0)
+            for (int k = 0; k < top; ++k) wt[k] = chosen_v[k] / (den + 1e-20f) * out_scale;
+        return;
+    }
     for (int k = 0; k < top; ++k) {
         float bv = -INFINITY;
         int bi = 0x7fffffff;
@@ -158,16 +200,18 @@ __global__ void __launch_bounds__(WARPS * 32) moe_route_kernel(const TA* x, int 
 // a warp a token, its row of logits in shared memory.
 template <int WARPS>
 __global__ void __launch_bounds__(WARPS * 32) moe_select_kernel(const float* __restrict__ z, int ldz, const void* __restrict__ bias, int b_kind,
-                                                               int* __restrict__ idx, float* __restrict__ wt, int T, int E, int top) {
+                                                               int* __restrict__ idx, float* __restrict__ wt, int T, int E, int top, int rule,
+                                                               float out_scale) {
     extern __shared__ __align__(16) float sm[];   // [WARPS][E]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x * WARPS + warp;
     il_pdl_begin();
     if (t >= T) return;
     float* zs = sm + (size_t)warp * E;
-    for (int e = lane; e < E; e += 32) zs[e] = z[(size_t)t * ldz + e] + (bias ? il_load_any(bias, b_kind, e) : 0.f);
+    // (rule 1: the bias is no part of the logits; it joins the scores where the experts are chosen)
+    for (int e = lane; e < E; e += 32) zs[e] = z[(size_t)t * ldz + e] + ((bias && rule == 0) ? il_load_any(bias, b_kind, e) : 0.f);
     __syncwarp();
-    moe_pick(zs, E, top, idx + (size_t)t * top, wt + (size_t)t * top, lane);
+    moe_pick(zs, E, top, idx + (size_t)t * top, wt + (size_t)t * top, lane, rule, bias, b_kind, out_scale);
 }
 
 // The body of the sort, by one whole block; `sh`: 2 * E ints of shared memory. (idx is not declared __restrict__: the
@@ -267,16 +311,17 @@ __global__ void __launch_bounds__(ML_WARPS * 32) moe_logits_kernel(const __nv_bf
 }
 
 // Chooses for every token (a warp a token, in turns) from logits z [T, E], then sorts the slots: one block.
-__global__ void __launch_bounds__(1024) moe_select_sort_kernel(const float* z, int* idx, float* __restrict__ wt, int T, int E, int top,
-                                                               int* __restrict__ group_off, int* __restrict__ pos_of_slot, int* __restrict__ row_of_pos) {
+__global__ void __launch_bounds__(1024) moe_select_sort_kernel(const float* z, int ldz, int* idx, float* __restrict__ wt, int T, int E, int top,
+                                                               int* __restrict__ group_off, int* __restrict__ pos_of_slot, int* __restrict__ row_of_pos,
+                                                               int rule, const void* __restrict__ corr, int c_kind, float out_scale) {
     extern __shared__ __align__(16) float sm[];   // [32][E] logits of the warps' tokens, then 2 * E ints for the sort
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     il_pdl_begin();
     float* zs = sm + (size_t)warp * E;
     for (int t = warp; t < T; t += 32) {
-        for (int e = lane; e < E; e += 32) zs[e] = z[(size_t)t * E + e];
+        for (int e = lane; e < E; e += 32) zs[e] = z[(size_t)t * ldz + e];
         __syncwarp();
-        moe_pick(zs, E, top, idx + (size_t)t * top, wt + (size_t)t * top, lane);
+        moe_pick(zs, E, top, idx + (size_t)t * top, wt + (size_t)t * top, lane, rule, corr, c_kind, out_scale);
         __syncwarp();
     }
     __syncthreads();                              // the choices, written to memory by this block's warps, are read below
@@ -299,29 +344,35 @@ __device__ __forceinline__ void st4c(__nv_bfloat16* p, float4 v) {
 
 // One block a token; a thread sums four neighbouring columns (H a multiple of 4: `vec`), the token's rows one after the
 // other in the order of its choices, so the sum does not depend on the number of threads or on the batch.
+// Experts without weights ("identity": the experts from n_real on, whose places in the sorted order start at
+// group_off[n_real]) return their input: such a choice adds weight * x[t] (`x` [T, ldx], the rows the experts read).
+// `sgate` (or null): one f32 number per token (stride ld_sg) whose sigmoid multiplies the shared row.
 template <typename TA>
 __global__ void moe_combine_kernel(const TA* y, const int* pos_of_slot, const float* wt, const TA* shared_rows, TA* __restrict__ out,
-                                   int H, int top, int vec) {
+                                   int H, int top, int vec, const int* group_off, int n_real, const TA* x, int ldx, const float* sgate,
+                                   int ld_sg) {
     __shared__ int sp[MOE_MAX_TOP];
     __shared__ float sw[MOE_MAX_TOP];
     const int t = blockIdx.x;
     il_pdl_begin();
     if (threadIdx.x < top) {                      // the token's places and weights once, not once per column
-        sp[threadIdx.x] = pos_of_slot[(size_t)t * top + threadIdx.x];
+        const int p = pos_of_slot[(size_t)t * top + threadIdx.x];
+        sp[threadIdx.x] = (group_off && p >= group_off[n_real]) ? -1 : p;       // -1: the input row itself
         sw[threadIdx.x] = wt[(size_t)t * top + threadIdx.x];
     }
     __syncthreads();
+    const float sg = (shared_rows && sgate) ? 1.f / (1.f + expf(-sgate[(size_t)t * ld_sg])) : 1.f;
     if (vec) {
         for (int h = threadIdx.x * 4; h < H; h += blockDim.x * 4) {
             float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
             for (int k = 0; k < top; ++k) {
-                const float4 v = ld4c(y + (size_t)sp[k] * H + h);
+                const float4 v = sp[k] >= 0 ? ld4c(y + (size_t)sp[k] * H + h) : ld4c(x + (size_t)t * ldx + h);
                 const float w = sw[k];
                 s.x = fmaf(w, v.x, s.x), s.y = fmaf(w, v.y, s.y), s.z = fmaf(w, v.z, s.z), s.w = fmaf(w, v.w, s.w);
             }
             if (shared_rows) {
                 const float4 v = ld4c(shared_rows + (size_t)t * H + h);
-                s.x += v.x, s.y += v.y, s.z += v.z, s.w += v.w;
+                s.x = fmaf(sg, v.x, s.x), s.y = fmaf(sg, v.y, s.y), s.z = fmaf(sg, v.z, s.z), s.w = fmaf(sg, v.w, s.w);
             }
             st4c(out + (size_t)t * H + h, s);
         }
@@ -329,8 +380,8 @@ __global__ void moe_combine_kernel(const TA* y, const int* pos_of_slot, const fl
     }
     for (int h = threadIdx.x; h < H; h += blockDim.x) {
         float s = 0.f;
-        for (int k = 0; k < top; ++k) s = fmaf(sw[k], il_to_f(y[(size_t)sp[k] * H + h]), s);
-        if (shared_rows) s += il_to_f(shared_rows[(size_t)t * H + h]);
+        for (int k = 0; k < top; ++k) s = fmaf(sw[k], il_to_f(sp[k] >= 0 ? y[(size_t)sp[k] * H + h] : x[(size_t)t * ldx + h]), s);
+        if (shared_rows) s = fmaf(sg, il_to_f(shared_rows[(size_t)t * H + h]), s);
         out[(size_t)t * H + h] = il_from_f<TA>(s);
     }
 }
@@ -457,9 +508,12 @@ IL_EXPORT int il_moe_route(const void* x, int act_kind, int ldx, const void* w, 
     return IL_BAD_ARG;
 }
 
-IL_EXPORT int il_moe_select(const float* z, int ldz, const void* bias, int b_kind, int* idx, float* wt, int T, int E, int top, cudaStream_t stream) {
+// rule 0: the `top` largest of z + bias, weights their softmax. rule 1: scores softmax(z) over all E, the largest score + bias
+// chosen, weights the chosen scores over their sum, times out_scale (see moe_pick).
+IL_EXPORT int il_moe_select(const float* z, int ldz, const void* bias, int b_kind, int* idx, float* wt, int T, int E, int top, int rule,
+                            float out_scale, cudaStream_t stream) {
     if (T <= 0) return IL_OK;
-    if (E <= 0 || top <= 0 || top > E || top > MOE_MAX_TOP || ldz < E) return IL_BAD_ARG;
+    if (E <= 0 || top <= 0 || top > E || top > MOE_MAX_TOP || ldz < E || (rule != 0 && rule != 1)) return IL_BAD_ARG;
     constexpr int WARPS = 8;
     const size_t smem = (size_t)WARPS * E * sizeof(float);
     if (smem > 200 * 1024) return IL_UNSUPPORTED;
@@ -467,27 +521,33 @@ IL_EXPORT int il_moe_select(const float* z, int ldz, const void* bias, int b_kin
         cudaError_t e = cudaFuncSetAttribute(moe_select_kernel<WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return 1000 + (int)e;
     }
-    IL_LAUNCH(moe_select_kernel<WARPS>, (T + WARPS - 1) / WARPS, WARPS * 32, smem, stream, z, ldz, bias, b_kind, idx, wt, T, E, top);
+    IL_LAUNCH(moe_select_kernel<WARPS>, (T + WARPS - 1) / WARPS, WARPS * 32, smem, stream, z, ldz, bias, b_kind, idx, wt, T, E, top, rule, out_scale);
     IL_LAUNCH_CHECK();
     return IL_OK;
 }
 
-// Router and sort of a few bfloat16 rows (a decode step): logits z [T, E] (scratch), then the choice and the sort in one
+// Router and sort of a few bfloat16 rows (a decode step): logits z [T, E + extra] (scratch), then the choice and the sort in one
 // block. IL_UNSUPPORTED where the rows are not whole 16-byte chunks or the experts' logits do not fit a block's memory.
+// `extra`: rows of `w` behind the E experts' whose products are written to z as further columns and take no part in the
+// choice (a gate that is a function of the same rows). rule, out_scale: see il_moe_select.
 IL_EXPORT int il_moe_route_sort_small(const void* x, int ldx, const void* w, const void* bias, int b_kind, float* z, int* idx, float* wt, int T, int H,
                                       int E, int top, const float* sumsq, int n_partial, float eps, float* rstd_out, int* group_off,
-                                      int* pos_of_slot, int* row_of_pos, cudaStream_t stream) {
+                                      int* pos_of_slot, int* row_of_pos, int extra, int rule, float out_scale, cudaStream_t stream) {
     if (T <= 0) return IL_OK;
-    if (H <= 0 || E <= 0 || top <= 0 || top > E || top > MOE_MAX_TOP || (sumsq && n_partial <= 0)) return IL_BAD_ARG;
+    if (H <= 0 || E <= 0 || top <= 0 || top > E || top > MOE_MAX_TOP || (sumsq && n_partial <= 0) || extra < 0 || (rule != 0 && rule != 1) ||
+        (extra > 0 && bias && rule == 0))
+        return IL_BAD_ARG;
     const size_t smem = (size_t)32 * E * sizeof(float) + (size_t)2 * E * sizeof(int);
     if (H % 8 || ldx % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || smem > 200 * 1024 || T > 65535) return IL_UNSUPPORTED;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(moe_select_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return 1000 + (int)e;
     }
-    IL_LAUNCH(moe_logits_kernel, dim3((E + ML_WARPS - 1) / ML_WARPS, T), ML_WARPS * 32, 0, stream, (const __nv_bfloat16*)x, ldx,
-              (const __nv_bfloat16*)w, bias, b_kind, z, T, H, E, sumsq, n_partial, 1.f / (float)H, eps, rstd_out);
-    IL_LAUNCH(moe_select_sort_kernel, 1, 1024, smem, stream, (const float*)z, idx, wt, T, E, top, group_off, pos_of_slot, row_of_pos);
+    const int EZ = E + extra;                     // the logits kernel knows no experts: it writes one column per row of w
+    IL_LAUNCH(moe_logits_kernel, dim3((EZ + ML_WARPS - 1) / ML_WARPS, T), ML_WARPS * 32, 0, stream, (const __nv_bfloat16*)x, ldx,
+              (const __nv_bfloat16*)w, rule == 0 ? bias : (const void*)nullptr, b_kind, z, T, H, EZ, sumsq, n_partial, 1.f / (float)H, eps, rstd_out);
+    IL_LAUNCH(moe_select_sort_kernel, 1, 1024, smem, stream, (const float*)z, EZ, idx, wt, T, E, top, group_off, pos_of_slot, row_of_pos, rule,
+              rule == 1 ? bias : (const void*)nullptr, b_kind, out_scale);
     IL_LAUNCH_CHECK();
     return IL_OK;
 }
@@ -502,16 +562,19 @@ IL_EXPORT int il_moe_sort(const int* idx, int n_slots, int top, int E, int* grou
 }
 
 IL_EXPORT int il_moe_combine(const void* y, int act_kind, const int* pos_of_slot, const float* wt, const void* shared_rows, void* out, int T,
-                             int H, int top, cudaStream_t stream) {
+                             int H, int top, const int* group_off, int n_real, const void* x, int ldx, const float* sgate, int ld_sg,
+                             cudaStream_t stream) {
     if (T <= 0) return IL_OK;
-    if (H <= 0 || top <= 0) return IL_BAD_ARG;
-    const int vec = (H % 4 == 0 && !((uintptr_t)y & 15) && !((uintptr_t)out & 15) && !((uintptr_t)shared_rows & 15)) ? 1 : 0;
+    if (H <= 0 || top <= 0 || (group_off && (!x || n_real < 0 || ldx < H))) return IL_BAD_ARG;
+    const int vec = (H % 4 == 0 && !((uintptr_t)y & 15) && !((uintptr_t)out & 15) && !((uintptr_t)shared_rows & 15) &&
+                     (!group_off || (ldx % 4 == 0 && !((uintptr_t)x & 15)))) ? 1 : 0;
     const int threads = vec ? (H >= 2048 ? 512 : H >= 1024 ? 256 : 128) : (H >= 1024 ? 256 : 128);
     if (act_kind == IL_F32)
-        IL_LAUNCH(moe_combine_kernel<float>, T, threads, 0, stream, (const float*)y, pos_of_slot, wt, (const float*)shared_rows, (float*)out, H, top, vec);
+        IL_LAUNCH(moe_combine_kernel<float>, T, threads, 0, stream, (const float*)y, pos_of_slot, wt, (const float*)shared_rows, (float*)out, H, top, vec,
+                  group_off, n_real, (const float*)x, ldx, sgate, ld_sg);
     else if (act_kind == IL_BF16)
         IL_LAUNCH(moe_combine_kernel<__nv_bfloat16>, T, threads, 0, stream, (const __nv_bfloat16*)y, pos_of_slot, wt,
-                  (const __nv_bfloat16*)shared_rows, (__nv_bfloat16*)out, H, top, vec);
+                  (const __nv_bfloat16*)shared_rows, (__nv_bfloat16*)out, H, top, vec, group_off, n_real, (const __nv_bfloat16*)x, ldx, sgate, ld_sg);
     else
         return IL_BAD_ARG;
     IL_LAUNCH_CHECK();

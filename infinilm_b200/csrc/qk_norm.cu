@@ -210,3 +210,87 @@ IL_EXPORT int il_gate_pack(const void* y, int act_kind, int hd, const void* gate
     IL_LAUNCH_CHECK();
     return IL_OK;
 }
+
+// ---- queries and keys normed over the whole projection, then rotated ---------------------------------------------------
+// Per token: the nh * dk query columns are divided by THEIR root mean square, all heads together, and multiplied by a
+// weight of that many entries; the nkv * dk key columns likewise. Then, of every head, the first `rot` dimensions turn by
+// angle = pos * inv_freq[i], dimension i paired with i + rot / 2 ((u, v) -> (u cos - v sin, v cos + u sin)); the others
+// pass. Queries go to q_out [T, nh * hd], keys to the K plane of the token's cache slot, values to the V plane, heads laid
+// out at hd columns with the surplus zero. k_off < 0: no keys or values (the mixer reads another layer's cache).
+// Sums of squares, angles and the rotation are f32. One block per token.
+template <typename TA>
+__global__ void qk_rows_norm_rope_store_kernel(const TA* proj, int ld, int q_off, int k_off, int v_off, int nh, int nkv, int dk, int dv, int hd,
+                                               const void* __restrict__ wq, const void* __restrict__ wk, int w_kind, float eps, int rot,
+                                               const float* __restrict__ inv_freq, TA* __restrict__ q_out,
+                                               const int* __restrict__ tok_pos, const int* __restrict__ tok_entry,
+                                               const int* __restrict__ block_table, int bt_stride, TA* __restrict__ cache, int page_size) {
+    __shared__ float red[32];
+    const int t = blockIdx.x;
+    const int pos = tok_pos[t];
+    const bool has_k = k_off >= 0;
+    int page = -1;
+    if (has_k && cache) page = block_table[(size_t)tok_entry[t] * bt_stride + pos / page_size];
+    il_pdl_wait();
+    const TA* row = proj + (size_t)t * ld;
+    const int nq = nh * dk, nk = nkv * dk, half = rot >> 1;
+    float sq = 0.f, sk = 0.f;
+    for (int i = threadIdx.x; i < nq; i += blockDim.x) {
+        const float x = il_to_f(row[q_off + i]);
+        sq += x * x;
+    }
+    if (has_k)
+        for (int i = threadIdx.x; i < nk; i += blockDim.x) {
+            const float x = il_to_f(row[k_off + i]);
+            sk += x * x;
+        }
+    sq = il_block_sum(sq, red);
+    sk = il_block_sum(sk, red);
+    const float rq = 1.f / sqrtf(sq / (float)nq + eps), rk = has_k ? 1.f / sqrtf(sk / (float)nk + eps) : 0.f;
+    // element d of head j of a normed and weighted projection, rotated
+    auto turned = [&](const TA* x, const void* w, float r, int j, int d) -> float {
+        const int c = j * dk + d;
+        const float a = il_to_f(x[c]) * r * il_load_any(w, w_kind, c);
+        if (d >= rot) return a;
+        const bool low = d < half;
+        const int c2 = low ? c + half : c - half;
+        const float b = il_to_f(x[c2]) * r * il_load_any(w, w_kind, c2);
+        float s, co;
+        sincosf((float)pos * inv_freq[low ? d : d - half], &s, &co);
+        return low ? a * co - b * s : a * co + b * s;
+    };
+    for (int idx = threadIdx.x; idx < nh * hd; idx += blockDim.x) {
+        const int j = idx / hd, d = idx - j * hd;
+        q_out[(size_t)t * nh * hd + idx] = il_from_f<TA>(d < dk ? turned(row + q_off, wq, rq, j, d) : 0.f);
+    }
+    if (page < 0) return;                         // no keys of its own, or no slot (the host reserves every page a step touches)
+    const size_t plane = (size_t)nkv * page_size * hd;
+    TA* kdst = cache + (size_t)page * 2 * plane + (size_t)(pos % page_size) * hd;
+    for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
+        const int g = idx / hd, d = idx - g * hd;
+        const size_t at = (size_t)g * page_size * hd + d;
+        kdst[at] = il_from_f<TA>(d < dk ? turned(row + k_off, wk, rk, g, d) : 0.f);
+        kdst[plane + at] = d < dv ? row[v_off + g * dv + d] : il_from_f<TA>(0.f);
+    }
+}
+
+IL_EXPORT int il_qk_rows_norm_rope_store(const void* proj, int act_kind, int ld, int q_off, int k_off, int v_off, int nh, int nkv, int dk, int dv,
+                                         int hd, const void* wq, const void* wk, int w_kind, float eps, int rot, const float* inv_freq,
+                                         void* q_out, const int* tok_pos, const int* tok_entry, const int* block_table, int bt_stride,
+                                         void* cache, int page_size, int T, cudaStream_t stream) {
+    if (T <= 0) return IL_OK;
+    if (nh <= 0 || nkv <= 0 || dk <= 0 || dv <= 0 || hd < dk || hd < dv || page_size <= 0 || !wq || (k_off >= 0 && !wk)) return IL_BAD_ARG;
+    if (rot < 0 || (rot & 1) || rot > dk || (rot > 0 && !inv_freq)) return IL_BAD_ARG;
+    const int work = nh * hd;
+    const int threads = work >= 2048 ? 512 : work >= 512 ? 256 : 128;
+    if (act_kind == IL_F32)
+        IL_LAUNCH(qk_rows_norm_rope_store_kernel<float>, T, threads, 0, stream, (const float*)proj, ld, q_off, k_off, v_off, nh, nkv, dk, dv, hd, wq,
+                  wk, w_kind, eps, rot, inv_freq, (float*)q_out, tok_pos, tok_entry, block_table, bt_stride, (float*)cache, page_size);
+    else if (act_kind == IL_BF16)
+        IL_LAUNCH(qk_rows_norm_rope_store_kernel<__nv_bfloat16>, T, threads, 0, stream, (const __nv_bfloat16*)proj, ld, q_off, k_off, v_off, nh, nkv,
+                  dk, dv, hd, wq, wk, w_kind, eps, rot, inv_freq, (__nv_bfloat16*)q_out, tok_pos, tok_entry, block_table, bt_stride,
+                  (__nv_bfloat16*)cache, page_size);
+    else
+        return IL_BAD_ARG;
+    IL_LAUNCH_CHECK();
+    return IL_OK;
+}

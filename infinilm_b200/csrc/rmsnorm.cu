@@ -240,3 +240,102 @@ IL_EXPORT int il_cast_rows(const float* x, void* out, int out_kind, long long to
     IL_LAUNCH_CHECK();
     return IL_OK;
 }
+
+// ---- several copies of the residual stream ("hyper-connections") ---------------------------------------------------------------
+// A model may keep S copies x_1 .. x_S of the residual stream (streams [T, S, H], f32). A sublayer reads u = sum_s in[s] x_s
+// through a norm, and its output y goes back as x_t <- sum_s mix[s, t] x_s + out[t] y, every new copy from the old ones.
+// One kernel does what lies between two sublayers, for one row a block:
+//   init (or null):   x_s = init[r] for every s           (the copies start as the embedding's output)
+//   y (or null):      the write-back of the sublayer before, with mix [S, S] (from, to) and out [S]
+//   in_next (or null): u = sum_t in_next[t] x_t, normed = u / sqrt(mean(u^2) + eps) * w   -> normed[r] (the next sublayer's input)
+//   sum_out (or null): sum_out[r] = sum_t x_t              (the stream as one row: what the model's last norm reads)
+// Everything is f32 but y (read) and normed (written), which have the compute dtype. S <= HC_MAX_STREAMS.
+// Dynamic shared memory: H floats (u between its two passes).
+#define HC_MAX_STREAMS 8
+template <typename TA>
+__global__ void hyper_step_kernel(float* streams, const float* init, const TA* y, const float* __restrict__ mix,
+                                  const float* __restrict__ out_w, const float* __restrict__ in_next, const void* __restrict__ w, int w_kind,
+                                  float eps, TA* __restrict__ normed, float* __restrict__ sum_out, int S, int H) {
+    extern __shared__ float us[];
+    __shared__ float red[32];
+    __shared__ float s_mix[HC_MAX_STREAMS * HC_MAX_STREAMS], s_out[HC_MAX_STREAMS], s_in[HC_MAX_STREAMS];
+    const int r = blockIdx.x;
+    if (threadIdx.x < S * S && y) s_mix[threadIdx.x] = mix[threadIdx.x];
+    if (threadIdx.x < S) {
+        if (y) s_out[threadIdx.x] = out_w[threadIdx.x];
+        if (in_next) s_in[threadIdx.x] = in_next[threadIdx.x];
+    }
+    il_pdl_wait();
+    __syncthreads();
+    float* xr = streams + (size_t)r * S * H;
+    float ss = 0.f;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        float x[HC_MAX_STREAMS], xn[HC_MAX_STREAMS];
+#pragma unroll
+        for (int s = 0; s < HC_MAX_STREAMS; ++s)
+            if (s < S) x[s] = init ? init[(size_t)r * H + h] : xr[(size_t)s * H + h];
+        if (y) {
+            const float yv = il_to_f(y[(size_t)r * H + h]);
+#pragma unroll
+            for (int t = 0; t < HC_MAX_STREAMS; ++t)
+                if (t < S) {
+                    float a = 0.f;
+#pragma unroll
+                    for (int s = 0; s < HC_MAX_STREAMS; ++s)
+                        if (s < S) a = fmaf(s_mix[s * S + t], x[s], a);
+                    xn[t] = fmaf(s_out[t], yv, a);
+                }
+        } else {
+#pragma unroll
+            for (int t = 0; t < HC_MAX_STREAMS; ++t)
+                if (t < S) xn[t] = x[t];
+        }
+        if (y || init) {
+#pragma unroll
+            for (int t = 0; t < HC_MAX_STREAMS; ++t)
+                if (t < S) xr[(size_t)t * H + h] = xn[t];
+        }
+        if (sum_out) {
+            float a = 0.f;
+#pragma unroll
+            for (int t = 0; t < HC_MAX_STREAMS; ++t)
+                if (t < S) a += xn[t];
+            sum_out[(size_t)r * H + h] = a;
+        }
+        if (in_next) {
+            float u = 0.f;
+#pragma unroll
+            for (int t = 0; t < HC_MAX_STREAMS; ++t)
+                if (t < S) u = fmaf(s_in[t], xn[t], u);
+            us[h] = u;
+            ss += u * u;
+        }
+    }
+    if (!in_next) return;
+    ss = il_block_sum(ss, red);
+    const float rstd = 1.f / sqrtf(ss / (float)H + eps);
+    for (int h = threadIdx.x; h < H; h += blockDim.x)
+        normed[(size_t)r * H + h] = il_from_f<TA>(us[h] * rstd * il_load_any(w, w_kind, h));
+}
+
+IL_EXPORT int il_hyper_step(float* streams, const float* init, const void* y, int act_kind, const float* mix, const float* out_w,
+                            const float* in_next, const void* w, int w_kind, float eps, void* normed, float* sum_out, int S, int H, int T,
+                            cudaStream_t stream) {
+    if (T <= 0) return IL_OK;
+    if (S <= 0 || S > HC_MAX_STREAMS || H <= 0 || (y && (!mix || !out_w)) || (in_next && (!w || !normed))) return IL_BAD_ARG;
+    const size_t smem = (size_t)H * sizeof(float);
+    if (smem > 200 * 1024) return IL_UNSUPPORTED;
+    const int threads = H >= 4096 ? 512 : H >= 1024 ? 256 : 128;
+    if (act_kind == IL_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(hyper_step_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        IL_LAUNCH(hyper_step_kernel<float>, T, threads, smem, stream, streams, init, (const float*)y, mix, out_w, in_next, w, w_kind, eps,
+                  (float*)normed, sum_out, S, H);
+    } else if (act_kind == IL_BF16) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(hyper_step_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        IL_LAUNCH(hyper_step_kernel<__nv_bfloat16>, T, threads, smem, stream, streams, init, (const __nv_bfloat16*)y, mix, out_w, in_next, w, w_kind,
+                  eps, (__nv_bfloat16*)normed, sum_out, S, H);
+    } else
+        return IL_BAD_ARG;
+    IL_LAUNCH_CHECK();
+    return IL_OK;
+}

@@ -257,6 +257,10 @@ IL_EXPORT int il_delta_prep(float* qk, int ld, int q_off, int k_off, int G, int 
 //                          weight; the state has one column more than v (vdim counts it), fed by the constant 1: it gathers
 //                          the weighted keys alone (the normaliser of a matrix memory), and the output's last column is its
 //                          product with q. v heads are vdim - 1 wide, the output's vdim.
+//   MODE 4 (channel decay): o = (S + diag(u_h) k v^T)^T q;  then  S = diag(w_t) S + k v^T   - a decay per token, head and key
+//                          channel (w: float32 rows of H * dim, row stride ld_g, passed as `gdec`), and a bonus u (float32
+//                          [H, dim], passed as `decay`) that lets the token's own k v^T into its read-out without entering
+//                          the state: the read-out comes BEFORE the state moves on.
 // q and k of SM_CHUNK tokens are staged in shared memory at a time. `in_act` 1: silu on q, k, v as they are read.
 // q/k head of value head h: h / (H / G). This form takes every size; key sizes up to 256 run the register form below
 // (`generic` 0), which gives the same sums in another order.
@@ -267,7 +271,7 @@ __global__ void matrix_state_scan_kernel(const float* __restrict__ q, const floa
                                          const float* __restrict__ decay, const float* __restrict__ beta, const float* __restrict__ gdec,
                                          float* state, size_t slot_stride, const int* __restrict__ read_slots,
                                          const int* __restrict__ write_slots, const int* __restrict__ qstart, float* __restrict__ out,
-                                         int ldo, int e0) {
+                                         int ldo, int e0, int ld_g) {
     extern __shared__ float sm[];
     const int ncol = blockDim.x;
     const int ncs = ncol + 1;
@@ -319,6 +323,14 @@ __global__ void matrix_state_scan_kernel(const float* __restrict__ q, const floa
                     S[d * ncs + threadIdx.x] = s;
                     o = fmaf(s, qq[d], o);
                 }
+            } else if (MODE == 4) {
+                const float* ww = gdec + row * ld_g + (size_t)h * dim;
+                const float* uu = decay + (size_t)h * dim;
+                for (int d = 0; d < dim; ++d) {
+                    const float kv = kk[d] * vc, s = S[d * ncs + threadIdx.x];
+                    o = fmaf(qq[d], fmaf(uu[d], kv, s), o);
+                    S[d * ncs + threadIdx.x] = fmaf(ww[d], s, kv);
+                }
             } else {
                 const float g = gdec[row * H + h], bt = beta[row * H + h];
                 float sk = 0.f;
@@ -358,7 +370,8 @@ __global__ void __launch_bounds__(SR_THREADS) matrix_state_scan_reg_kernel(
     const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, int ld_q, int ld_k, int ld_v, int H, int G,
     int dim, int vdim, int in_act, const float* __restrict__ decay, const float* __restrict__ beta, const float* __restrict__ gdec,
     float* state, size_t slot_stride, const int* __restrict__ read_slots, const int* __restrict__ write_slots,
-    const int* __restrict__ qstart, float* __restrict__ out, int ldo, int log_split, int e0, int n_ent, int seg_len, float* seg_state) {
+    const int* __restrict__ qstart, float* __restrict__ out, int ldo, int log_split, int e0, int n_ent, int seg_len, float* seg_state,
+    int ld_g) {
     extern __shared__ float sm[];
     constexpr int LOG_DPT = DPT == 8 ? 3 : DPT == 16 ? 4 : 5;
     constexpr int SEG = DPT + 4;                  // a lane's DPT values of q (or k) and 4 floats of padding: the lanes of a column then
@@ -370,6 +383,7 @@ __global__ void __launch_bounds__(SR_THREADS) matrix_state_scan_reg_kernel(
     float* ks = qs + SR_CHUNK * row_f;            // [SR_CHUNK][split][SEG]
     float* vs = ks + SR_CHUNK * row_f;            // [SR_CHUNK][cpb]
     float* gb = vs + SR_CHUNK * cpb;              // [2][SR_CHUNK]: g, beta
+    float* wsm = gb + ((2 * SR_CHUNK + 3) & ~3);  // MODE 4: [SR_CHUNK][split][SEG], the decays of the key channels, laid out as k
     const int h = blockIdx.y, tid = threadIdx.x;
     const int part = tid & (split - 1), col_l = tid >> log_split, c = blockIdx.z * cpb + col_l;
     // Which tokens this block walks. Plain form (seg_len 0): entry e0 + blockIdx.x, all of it. Segmented form (the decayed
@@ -457,7 +471,12 @@ __global__ void __launch_bounds__(SR_THREADS) matrix_state_scan_reg_kernel(
     constexpr int NQ = (DPT * SR_MAX_SPLIT + TPT - 1) / TPT;       // q (and k) values per thread at the widest split
     constexpr int NV = (SR_THREADS + TPT - 1) / TPT;               // v values per thread at split 1
     static_assert(TPT >= DPT, "a staging thread's entries must fall into whole lane segments");
-    float qr[NQ], kr[NQ], vr[NV], gr = 0.f;
+    float qr[NQ], kr[NQ], vr[NV], gr = 0.f, wr_[MODE == 4 ? NQ : 1];
+    float U[MODE == 4 ? DPT : 1];                 // MODE 4: the bonus of this lane's key channels
+    if (MODE == 4) {
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) U[i] = d0 + i < dim ? decay[(size_t)h * dim + d0 + i] : 0.f;
+    }
     const int s_tt = tid / TPT, s_l = tid % TPT;
     const int s_at = s_tt * row_f + (s_l >> LOG_DPT) * SEG + (s_l & (DPT - 1));   // + j * (TPT >> LOG_DPT) * SEG
 
@@ -471,6 +490,7 @@ __global__ void __launch_bounds__(SR_THREADS) matrix_state_scan_reg_kernel(
             const bool ok = tok && s_l + j * TPT < dim;
             qr[j] = ok ? qp[j * TPT] : 0.f;
             kr[j] = (MODE != 2 && ok) ? kp[j * TPT] : 0.f;
+            if (MODE == 4) wr_[j] = ok ? gdec[row * ld_g + (size_t)h * dim + s_l + j * TPT] : 0.f;
         }
         if (MODE == 3) {                          // v heads are vdim - 1 wide; the state's last column is fed by the constant 1
             const float* vp = v + row * ld_v + h * (vdim - 1) + blockIdx.z * cpb + s_l;
@@ -496,6 +516,7 @@ __global__ void __launch_bounds__(SR_THREADS) matrix_state_scan_reg_kernel(
             if (s_l + j * TPT < dimp) {
                 qs[s_at + j * (TPT >> LOG_DPT) * SEG] = in_act ? sm_silu_fast(qr[j]) : qr[j];
                 if (MODE != 2) ks[s_at + j * (TPT >> LOG_DPT) * SEG] = in_act ? sm_silu_fast(kr[j]) : kr[j];
+                if (MODE == 4) wsm[s_at + j * (TPT >> LOG_DPT) * SEG] = wr_[j];
             }
         if (MODE != 2) {
 #pragma unroll
@@ -544,6 +565,19 @@ __global__ void __launch_bounds__(SR_THREADS) matrix_state_scan_reg_kernel(
                         S[4 * i + 3] = fmaf(dec, S[4 * i + 3], k4.w * vc);
                         o0 = fmaf(S[4 * i], q4.x, o0), o1 = fmaf(S[4 * i + 1], q4.y, o1);
                         o2 = fmaf(S[4 * i + 2], q4.z, o2), o3 = fmaf(S[4 * i + 3], q4.w, o3);
+                    }
+                } else if (MODE == 4) {
+                    // the read-out first (the state before this token, plus the token's own k v^T weighted by the bonus), then
+                    // the state moves on under this token's decays
+                    const float4* ww = reinterpret_cast<const float4*>(wsm + tt * row_f + part * SEG);
+#pragma unroll
+                    for (int i = 0; i < DPT / 4; ++i) {
+                        const float4 k4 = kk[i], q4 = qq[i], w4 = ww[i];
+                        const float a0 = k4.x * vc, a1 = k4.y * vc, a2 = k4.z * vc, a3 = k4.w * vc;
+                        o0 = fmaf(q4.x, fmaf(U[4 * i], a0, S[4 * i]), o0), o1 = fmaf(q4.y, fmaf(U[4 * i + 1], a1, S[4 * i + 1]), o1);
+                        o2 = fmaf(q4.z, fmaf(U[4 * i + 2], a2, S[4 * i + 2]), o2), o3 = fmaf(q4.w, fmaf(U[4 * i + 3], a3, S[4 * i + 3]), o3);
+                        S[4 * i] = fmaf(w4.x, S[4 * i], a0), S[4 * i + 1] = fmaf(w4.y, S[4 * i + 1], a1);
+                        S[4 * i + 2] = fmaf(w4.z, S[4 * i + 2], a2), S[4 * i + 3] = fmaf(w4.w, S[4 * i + 3], a3);
                     }
                 } else if (MODE == 3) {
                     const float g = gb[tt], u = gb[SR_CHUNK + tt] * vc;
@@ -622,10 +656,10 @@ template <int MODE, int DPT, int CH, int MS>
 static void sr_launch(dim3 grid, size_t smem, cudaStream_t stream, const float* q, const float* k, const float* v, int ld_q, int ld_k, int ld_v,
                       int H, int G, int dim, int vdim, int in_act, const float* decay, const float* beta, const float* gdec, float* state,
                       size_t slot_stride, const int* read_slots, const int* write_slots, const int* qstart, float* out, int ldo, int log_split,
-                      int e0, int n_ent, int seg_len, float* seg_state) {
+                      int e0, int n_ent, int seg_len, float* seg_state, int ld_g) {
     matrix_state_scan_reg_kernel<MODE, DPT, CH, MS><<<grid, SR_THREADS, smem, stream>>>(q, k, v, ld_q, ld_k, ld_v, H, G, dim, vdim, in_act, decay, beta,
                                                                                     gdec, state, slot_stride, read_slots, write_slots, qstart, out,
-                                                                                    ldo, log_split, e0, n_ent, seg_len, seg_state);
+                                                                                    ldo, log_split, e0, n_ent, seg_len, seg_state, ld_g);
 }
 
 // In place: x[t, c] = silu(x[t, c]) for the first `cols` columns of float32 rows (the recurrences' inputs, as a pass of its own).
@@ -649,15 +683,17 @@ IL_EXPORT int il_matrix_state_scan(int mode, const float* q, const float* k, con
                                    int dim, int vdim, int in_act, const float* decay, const float* beta, const float* gdec, float* state,
                                    long long slot_stride, const int* read_slots, const int* write_slots, const int* qstart, int E,
                                    float* out, int ldo, int generic, int e0, int single, int seg_len, int n_tiles, float* seg_state,
-                                   cudaStream_t stream) {
+                                   int ld_g, cudaStream_t stream) {
+    // mode 4: `gdec` holds the decays per token and key channel (float32 rows of H * dim, row stride ld_g), `decay` the bonus
+    // [H, dim]; G = H.
     if (E <= 0) return IL_OK;
     if (e0 < 0) return IL_BAD_ARG;
     // seg_len > 0 (decayed sum, register form only): the entries' tokens in segments of seg_len, n_tiles of them at most
     // (a bound is enough), seg_state float32 [n_tiles, H, vdim, dim] scratch; two passes.
     if (seg_len > 0 && (mode != 0 || generic || single || dim > 256 || n_tiles <= 0 || !seg_state || seg_len % 8)) return IL_BAD_ARG;
-    if (H <= 0 || G <= 0 || H % G || dim <= 0 || vdim <= 0 || (mode != 0 && mode != 1 && mode != 3)) return IL_BAD_ARG;
+    if (H <= 0 || G <= 0 || H % G || dim <= 0 || vdim <= 0 || (mode != 0 && mode != 1 && mode != 3 && mode != 4)) return IL_BAD_ARG;
     if (mode == 3 && (vdim < 2 || in_act)) return IL_BAD_ARG;
-    if (mode == 0 ? !decay : (!beta || !gdec)) return IL_BAD_ARG;
+    if (mode == 4 ? (!decay || !gdec || G != H || in_act || ld_g < H * dim) : mode == 0 ? !decay : (!beta || !gdec)) return IL_BAD_ARG;
     if (dim <= 256 && !generic) {
         // Rows of a column per lane (8 or 16) and lanes per column (a power of two up to 16) that cover dim. Few blocks (one
         // long prompt) of the decayed sum take the narrower lanes: twice the warps, each with half the products per token
@@ -672,10 +708,10 @@ IL_EXPORT int il_matrix_state_scan(int mode, const float* q, const float* k, con
         while ((dpt << log_split) < dim) ++log_split;
         const int cpb = SR_THREADS >> log_split;
         const int ch = single ? 1 : 8;
-        const size_t smem_r = ((size_t)ch * (2 * ((dpt + 4) << log_split) + cpb) + 2 * ch) * sizeof(float);
+        const size_t smem_r = ((size_t)ch * ((mode == 4 ? 3 : 2) * ((dpt + 4) << log_split) + cpb) + ((2 * ch + 3) & ~3)) * sizeof(float);
         const dim3 grid_r(seg_len > 0 ? n_tiles : E, H, (vdim + cpb - 1) / cpb);
 #define SR_ARGS grid_r, smem_r, stream, q, k, v, ld_q, ld_k, ld_v, H, G, dim, vdim, in_act, decay, beta, gdec, state, (size_t)slot_stride, \
-                read_slots, write_slots, qstart, out, ldo, log_split, e0, E, seg_len, seg_state
+                read_slots, write_slots, qstart, out, ldo, log_split, e0, E, seg_len, seg_state, ld_g
         // (the widest split a variant is built for sizes its staging registers: 8 lanes up to dim = 8 DPT, 16 beyond)
 #define SR_PICK(MODE_, DPT_)                                                                                     \
         do {                                                                                                     \
@@ -691,6 +727,8 @@ IL_EXPORT int il_matrix_state_scan(int mode, const float* q, const float* k, con
             }
         } else if (mode == 1) {
             if (dpt == 8) SR_PICK(1, 8); else SR_PICK(1, 16);
+        } else if (mode == 4) {
+            if (dpt == 8) SR_PICK(4, 8); else SR_PICK(4, 16);
         } else {
             if (dpt == 8) SR_PICK(3, 8); else SR_PICK(3, 16);
         }
@@ -705,18 +743,22 @@ IL_EXPORT int il_matrix_state_scan(int mode, const float* q, const float* k, con
     }
     if (smem > 200 * 1024) return IL_UNSUPPORTED;
     const dim3 grid(E, H, (vdim + ncol - 1) / ncol);
-    if (mode == 3) {
+    if (mode == 4) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(matrix_state_scan_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        matrix_state_scan_kernel<4><<<grid, ncol, smem, stream>>>(q, k, v, ld_q, ld_k, ld_v, H, G, dim, vdim, in_act, decay, beta, gdec, state,
+                                                                  (size_t)slot_stride, read_slots, write_slots, qstart, out, ldo, e0, ld_g);
+    } else if (mode == 3) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(matrix_state_scan_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         matrix_state_scan_kernel<3><<<grid, ncol, smem, stream>>>(q, k, v, ld_q, ld_k, ld_v, H, G, dim, vdim, in_act, decay, beta, gdec, state,
-                                                                  (size_t)slot_stride, read_slots, write_slots, qstart, out, ldo, e0);
+                                                                  (size_t)slot_stride, read_slots, write_slots, qstart, out, ldo, e0, ld_g);
     } else if (mode == 0) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(matrix_state_scan_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         matrix_state_scan_kernel<0><<<grid, ncol, smem, stream>>>(q, k, v, ld_q, ld_k, ld_v, H, G, dim, vdim, in_act, decay, beta, gdec, state,
-                                                                  (size_t)slot_stride, read_slots, write_slots, qstart, out, ldo, e0);
+                                                                  (size_t)slot_stride, read_slots, write_slots, qstart, out, ldo, e0, ld_g);
     } else {
         if (smem > 48 * 1024) cudaFuncSetAttribute(matrix_state_scan_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         matrix_state_scan_kernel<1><<<grid, ncol, smem, stream>>>(q, k, v, ld_q, ld_k, ld_v, H, G, dim, vdim, in_act, decay, beta, gdec, state,
-                                                                  (size_t)slot_stride, read_slots, write_slots, qstart, out, ldo, e0);
+                                                                  (size_t)slot_stride, read_slots, write_slots, qstart, out, ldo, e0, ld_g);
     }
     IL_LAUNCH_CHECK();
     return IL_OK;
@@ -925,6 +967,88 @@ IL_EXPORT int il_softcap(float* y, float cap, long long total, cudaStream_t stre
     if (total <= 0) return IL_OK;
     if (!(cap > 0.f)) return IL_BAD_ARG;
     softcap_kernel<<<sm_grid((size_t)total, 256), 256, 0, stream>>>(y, cap, (size_t)total);
+    IL_LAUNCH_CHECK();
+    return IL_OK;
+}
+
+// ---- a token's input blended with its predecessor's ------------------------------------------------------------------------
+// out[t, m * W + c] = h[t, c] + (h[t - 1, c] - h[t, c]) * mu[m, c] for m < n_mix: every projection of a mixer reads its own blend
+// of the token's row and the row before it in the sequence. The row before a step's first token comes from the request's
+// state (float32 [W]; the zero slot for a sequence's first token), which then receives the entry's last row. Only the thread
+// of an entry's first token touches the state of its column - it reads before it writes - so an entry may read and write one
+// slot. Blends are computed in f32 and written in the rows' dtype. One thread per (token, column).
+template <typename TA>
+__global__ void token_shift_mix_kernel(const TA* __restrict__ h, int ldh, const float* __restrict__ mu, int n_mix, float* state,
+                                       size_t slot_stride, const int* __restrict__ read_slots, const int* __restrict__ write_slots,
+                                       const int* __restrict__ tok_entry, const int* __restrict__ qstart, TA* __restrict__ out, int ldo,
+                                       int W, int T) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= W) return;
+    for (int t = blockIdx.y; t < T; t += gridDim.y) {
+        const int e = tok_entry[t];
+        const int first = qstart[e];
+        const float cur = il_to_f(h[(size_t)t * ldh + c]);
+        float prev;
+        if (t == first) {
+            prev = state[(size_t)read_slots[e] * slot_stride + c];
+            if (write_slots) state[(size_t)write_slots[e] * slot_stride + c] = il_to_f(h[(size_t)(qstart[e + 1] - 1) * ldh + c]);
+        } else {
+            prev = il_to_f(h[(size_t)(t - 1) * ldh + c]);
+        }
+        const float d = prev - cur;
+        for (int m = 0; m < n_mix; ++m) out[(size_t)t * ldo + (size_t)m * W + c] = il_from_f<TA>(fmaf(d, mu[(size_t)m * W + c], cur));
+    }
+}
+
+IL_EXPORT int il_token_shift_mix(const void* h, int kind, int ldh, const float* mu, int n_mix, float* state, long long slot_stride,
+                                 const int* read_slots, const int* write_slots, const int* tok_entry, const int* qstart, void* out, int ldo,
+                                 int W, int T, cudaStream_t stream) {
+    if (T <= 0) return IL_OK;
+    if (W <= 0 || n_mix <= 0 || ldo < n_mix * W || slot_stride < W) return IL_BAD_ARG;
+    const dim3 grid((W + 127) / 128, T < 32768 ? T : 32768);
+    if (kind == IL_F32)
+        token_shift_mix_kernel<float><<<grid, 128, 0, stream>>>((const float*)h, ldh, mu, n_mix, state, (size_t)slot_stride, read_slots, write_slots,
+                                                                tok_entry, qstart, (float*)out, ldo, W, T);
+    else if (kind == IL_BF16)
+        token_shift_mix_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)h, ldh, mu, n_mix, state, (size_t)slot_stride, read_slots,
+                                                                        write_slots, tok_entry, qstart, (__nv_bfloat16*)out, ldo, W, T);
+    else
+        return IL_BAD_ARG;
+    IL_LAUNCH_CHECK();
+    return IL_OK;
+}
+
+// ---- a decay from its pre-activation: w = exp(-exp(z + w0)), float32 in place (z [T, ld], the first `cols` columns; w0 [cols]) ----
+__global__ void double_exp_decay_kernel(float* z, int ld, const float* __restrict__ w0, int cols, int T) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= cols) return;
+    const float b = w0 ? w0[c] : 0.f;
+    for (int t = blockIdx.y; t < T; t += gridDim.y) {
+        float* p = z + (size_t)t * ld + c;
+        *p = expf(-expf(*p + b));
+    }
+}
+
+IL_EXPORT int il_double_exp_decay(float* z, int ld, const float* w0, int cols, int T, cudaStream_t stream) {
+    if (T <= 0 || cols <= 0) return IL_OK;
+    double_exp_decay_kernel<<<dim3((cols + 255) / 256, T < 32768 ? T : 32768), 256, 0, stream>>>(z, ld, w0, cols, T);
+    IL_LAUNCH_CHECK();
+    return IL_OK;
+}
+
+// ---- out = tanh(x), float32 rows in, rows of the compute dtype out (the inner activation of a low-rank projection) ----------
+template <typename TO>
+__global__ void tanh_rows_kernel(const float* __restrict__ x, TO* __restrict__ out, size_t total) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x)
+        out[idx] = il_from_f<TO>(tanhf(x[idx]));
+}
+
+IL_EXPORT int il_tanh_rows(const float* x, void* out, int out_kind, long long total, cudaStream_t stream) {
+    if (total <= 0) return IL_OK;
+    const int grid = sm_grid((size_t)total, 256);
+    if (out_kind == IL_F32) tanh_rows_kernel<float><<<grid, 256, 0, stream>>>(x, (float*)out, (size_t)total);
+    else if (out_kind == IL_BF16) tanh_rows_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(x, (__nv_bfloat16*)out, (size_t)total);
+    else return IL_BAD_ARG;
     IL_LAUNCH_CHECK();
     return IL_OK;
 }

@@ -5,7 +5,7 @@ import importlib
 
 from .causal_lm import CausalLM
 
-BUILTIN = ("minicpm4", "nirozen", "gopitar", "somipel")
+BUILTIN = ("minicpm4", "nirozen", "gopitar", "somipel", "zokuzen")
 
 
 def register_builtin() -> None:

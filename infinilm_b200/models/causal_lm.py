@@ -104,7 +104,9 @@ class CausalLM:
             nxt_st = self.order[i + 1] if i + 1 < len(self.order) else None
             nxt = self.blocks[nxt_st.layer] if nxt_st is not None and nxt_st.add_row is None and not nxt_st.add_embedding else None
             kw = {"pre_add": emb_out} if st.add_embedding else {} if st.add_row is None else {"pre_add": self.pass_vectors.row(st.add_row)}
-            if blk.takes_next_norm and nxt is not None and nxt.accepts_normed_input(T):
+            if blk.takes_next_block:
+                pending = blk.run(resid, pending, ctx, caches[i], next_block=nxt, **kw)
+            elif blk.takes_next_norm and nxt is not None and nxt.accepts_normed_input(T):
                 pending = blk.run(resid, pending, ctx, caches[i], next_norm=nxt.mixer_norm, **kw)
             else:
                 pending = blk.run(resid, pending, ctx, caches[i], **kw)
@@ -114,7 +116,7 @@ class CausalLM:
         logits = ctx.ws.rows("logits", n, self.vocab, torch.float32)
         if n == 0:
             return logits
-        if isinstance(pending, ops.ResidualCopy):         # the last block added its branches itself
+        if isinstance(pending, ops.ResidualCopy) or getattr(pending, "nothing_pending", False):   # the last block added its branches itself
             pending = None
         branch, bscale = pending if pending is not None else (None, 1.0)
         normed = self.final_norm.add_norm(resid, branch, bscale, ctx.ws.rows("final_normed", n, self.hidden, self.dtype),

@@ -255,6 +255,44 @@ def norm_add(resid: torch.Tensor, branch: torch.Tensor, weight: torch.Tensor, ep
              _stream()), "norm_add")
 
 
+HYPER_MAX_STREAMS = 8
+
+
+def hyper_step(streams: torch.Tensor, n_streams: int, *, init: Optional[torch.Tensor] = None, y: Optional[torch.Tensor] = None,
+               mix: Optional[torch.Tensor] = None, out_w: Optional[torch.Tensor] = None, in_next: Optional[torch.Tensor] = None,
+               norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0, normed: Optional[torch.Tensor] = None,
+               sum_out: Optional[torch.Tensor] = None) -> None:
+    """What lies between two sublayers of a model that keeps `n_streams` copies of its residual stream (`streams` float32
+    [T, n_streams * H], in place), row by row in float32:
+    `init` (float32 [T, H]): every copy starts as this row; `y` [T, H] with `mix` [S, S] and `out_w` [S]: the write-back of the
+    sublayer before, x_t <- sum_s mix[s, t] x_s + out_w[t] y; `in_next` [S] with `norm_weight` and `normed` [T, H]: the next
+    sublayer's input, RMSNorm(sum_t in_next[t] x_t) * norm_weight; `sum_out` (float32 [T, H]): the sum of the copies."""
+    _need_cuda(streams, init, y, mix, out_w, in_next, norm_weight, normed, sum_out)
+    T, SH = streams.shape
+    S = int(n_streams)
+    if streams.dtype != torch.float32 or not streams.is_contiguous() or S < 1 or S > HYPER_MAX_STREAMS or SH % S:
+        raise KernelError(f"hyper_step: streams float32 [T, S * H] with 1 <= S <= {HYPER_MAX_STREAMS}")
+    H = SH // S
+    for name, t in (("init", init), ("sum_out", sum_out)):
+        if t is not None and (t.dtype != torch.float32 or tuple(t.shape) != (T, H) or not t.is_contiguous()):
+            raise KernelError(f"hyper_step: {name} float32 [T, H]")
+    for name, t, n in (("mix", mix, S * S), ("out_w", out_w, S), ("in_next", in_next, S)):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous()):
+            raise KernelError(f"hyper_step: {name} float32 with {n} entries")
+    if y is not None and (mix is None or out_w is None or tuple(y.shape) != (T, H) or not y.is_contiguous()):
+        raise KernelError("hyper_step: y [T, H] comes with mix and out_w")
+    if in_next is not None and (norm_weight is None or normed is None or norm_weight.numel() != H or tuple(normed.shape) != (T, H)
+                                or not normed.is_contiguous()):
+        raise KernelError("hyper_step: in_next comes with norm_weight [H] and normed [T, H]")
+    if y is not None and normed is not None and y.dtype != normed.dtype:
+        raise KernelError("hyper_step: y and normed have one dtype")
+    act = y.dtype if y is not None else normed.dtype if normed is not None else torch.float32
+    f = _fn("rmsnorm", "il_hyper_step", [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_float,
+                                         _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(_ptr(streams), _ptr(init), _ptr(y), kind_of(act), _ptr(mix), _ptr(out_w), _ptr(in_next), _ptr(norm_weight),
+             kind_of(norm_weight.dtype) if norm_weight is not None else 0, eps, _ptr(normed), _ptr(sum_out), S, H, T, _stream()), "hyper_step")
+
+
 def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
     """out = x rounded to bfloat16; x contiguous float32, out of the same shape."""
     _need_cuda(x, out)
@@ -295,6 +333,40 @@ def qk_norm_store(proj: torch.Tensor, q_off: int, k_off: Optional[int], v_off: i
     _check(f(_ptr(proj), kind_of(proj.dtype), proj.stride(0), q_off, k_off if has_k else -1, v_off, n_heads, n_kv_heads, qk_dim, v_dim,
              head_dim, _ptr(w_q), _ptr(w_k), kind_of(w_q.dtype), eps, temp_coef, temp_every, _ptr(q_out), _ptr(tok_pos), _ptr(tok_entry),
              _ptr(block_table), block_table.shape[1], _ptr(cache if has_k else None), page_size, T, _stream()), "qk_norm_store")
+
+
+def qk_rows_norm_rope_store(proj: torch.Tensor, q_off: int, k_off: Optional[int], v_off: int, n_heads: int, n_kv_heads: int, qk_dim: int,
+                            v_dim: int, head_dim: int, w_q: torch.Tensor, w_k: Optional[torch.Tensor], eps: float, rot_dim: int,
+                            inv_freq: Optional[torch.Tensor], q_out: torch.Tensor, tok_pos: torch.Tensor, tok_entry: torch.Tensor,
+                            block_table: torch.Tensor, cache: Optional[torch.Tensor], page_size: int) -> None:
+    """Per token: all query columns are divided by their common root mean square and multiplied by `w_q` [heads * qk_dim], all
+    key columns likewise with `w_k` [kv_heads * qk_dim]; then the first `rot_dim` dimensions of every head turn by
+    pos * inv_freq[i] (dimension i paired with i + rot_dim / 2). Queries to `q_out` [T, heads * head_dim], keys and values to
+    the K and V plane of the token's cache slot; heads laid out at head_dim, the surplus zero. `k_off` None: queries only."""
+    _need_cuda(proj, w_q, w_k, inv_freq, q_out, tok_pos, tok_entry, block_table, cache)
+    T = proj.shape[0]
+    has_k = k_off is not None
+    if proj.stride(1) != 1 or q_off + n_heads * qk_dim > proj.shape[1] or (has_k and (k_off + n_kv_heads * qk_dim > proj.shape[1]
+                                                                                    or v_off + n_kv_heads * v_dim > proj.shape[1])):
+        raise KernelError("qk_rows_norm_rope_store: segments lie outside the rows")
+    if w_q.numel() != n_heads * qk_dim or (has_k and (w_k is None or w_k.numel() != n_kv_heads * qk_dim or w_k.dtype != w_q.dtype)):
+        raise KernelError("qk_rows_norm_rope_store: norm weights of heads * qk_dim (queries) and kv_heads * qk_dim (keys) entries, one dtype")
+    if rot_dim and (inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() != rot_dim // 2 or rot_dim % 2 or rot_dim > qk_dim):
+        raise KernelError("qk_rows_norm_rope_store: inv_freq float32 [rot_dim / 2], rot_dim even and at most qk_dim")
+    if tuple(q_out.shape) != (T, n_heads * head_dim) or q_out.dtype != proj.dtype or not q_out.is_contiguous():
+        raise KernelError("qk_rows_norm_rope_store: q_out [T, heads * head_dim] of proj's dtype")
+    _i32("qk_rows_norm_rope_store", tok_pos, tok_entry, block_table)
+    _contig("block_table", block_table)
+    if has_k:
+        if cache is None or not cache.is_contiguous() or cache.dtype != proj.dtype or tuple(cache.shape[1:]) != (2, n_kv_heads, page_size, head_dim):
+            raise KernelError("qk_rows_norm_rope_store: cache [pages,2,kv_heads,page,head_dim] of proj's dtype")
+    f = _fn("qk_norm", "il_qk_rows_norm_rope_store", [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                                      _c_void_p, _c_void_p, _c_int, _c_float, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                                                      _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p])
+    _check(f(_ptr(proj), kind_of(proj.dtype), proj.stride(0), q_off, k_off if has_k else -1, v_off, n_heads, n_kv_heads, qk_dim, v_dim,
+             head_dim, _ptr(w_q), _ptr(w_k), kind_of(w_q.dtype), eps, rot_dim, _ptr(inv_freq if rot_dim else None), _ptr(q_out),
+             _ptr(tok_pos), _ptr(tok_entry), _ptr(block_table), block_table.shape[1], _ptr(cache if has_k else None), page_size, T,
+             _stream()), "qk_rows_norm_rope_store")
 
 
 def gate_pack(y: torch.Tensor, head_dim: int, gate: Optional[torch.Tensor], g_off: int, out: torch.Tensor, n_heads: int, v_dim: int) -> None:
@@ -528,6 +600,17 @@ class ResidualCopy:
 
     def __init__(self, rows: torch.Tensor):
         self.rows = rows
+
+
+class StreamSet:
+    """What a block of a model with several copies of its residual stream hands the next one: the copies (float32
+    [T, S * H], all write-backs done) and, if the block prepared it, the next block's first normed input. Nothing is pending;
+    the model's `resid` holds the copies' sum whenever `normed` is None."""
+    __slots__ = ("streams", "n_streams", "normed")
+    nothing_pending = True
+
+    def __init__(self, streams: torch.Tensor, n_streams: int, normed: Optional[torch.Tensor] = None):
+        self.streams, self.n_streams, self.normed = streams, n_streams, normed
 
 
 class NormedInput:
@@ -819,6 +902,7 @@ def sigmoid_gate(y: torch.Tensor, gate: torch.Tensor) -> None:
 
 
 MOE_MAX_TOP = 32
+ROUTE_TOP_LOGITS, ROUTE_SOFTMAX_ALL = 0, 1         # how a router's logits become choices and weights (`moe_select`)
 
 
 def moe_route(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], idx: torch.Tensor, wt: torch.Tensor, top: int,
@@ -852,17 +936,20 @@ def moe_route(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], id
 
 def moe_route_sort_small(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], z: torch.Tensor, idx: torch.Tensor, wt: torch.Tensor,
                          top: int, group_off: torch.Tensor, pos_of_slot: torch.Tensor, row_of_pos: torch.Tensor,
-                         norm_in: Optional["NormedInput"] = None, rstd_out: Optional[torch.Tensor] = None) -> None:
+                         norm_in: Optional["NormedInput"] = None, rstd_out: Optional[torch.Tensor] = None, extra: int = 0,
+                         rule: int = ROUTE_TOP_LOGITS, out_scale: float = 1.0) -> None:
     """`moe_route` and `moe_sort` for a few bfloat16 rows (a decode step) as two short kernels: the logits, a warp per
-    (token, expert), into z [T, E] float32; then one block that chooses for every token and sorts the slots.
-    Rows of whole 16-byte chunks (H a multiple of 8); `route_sort_small_ok` says whether a shape is taken."""
+    (token, expert), into z [T, E + extra] float32; then one block that chooses for every token and sorts the slots.
+    Rows of whole 16-byte chunks (H a multiple of 8); `route_sort_small_ok` says whether a shape is taken.
+    `extra`: the last rows of `w` are no experts - their products are written to z's last columns and take no part in the
+    choice. `rule`, `out_scale`: see `moe_select`."""
     _need_cuda(x, w, bias, z, idx, wt, group_off, pos_of_slot, row_of_pos, rstd_out)
     T, H = x.shape
-    E = w.shape[0]
+    E = w.shape[0] - extra
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.shape[1] != H or x.stride(1) != 1 or not w.is_contiguous():
         raise KernelError("moe_route_sort_small: bfloat16 x [T,H], w [E,H]")
-    if z.dtype != torch.float32 or z.numel() < T * E or not z.is_contiguous():
-        raise KernelError("moe_route_sort_small: z float32 [T, E]")
+    if z.dtype != torch.float32 or z.numel() < T * (E + extra) or not z.is_contiguous():
+        raise KernelError("moe_route_sort_small: z float32 [T, E + extra]")
     if idx.dtype != torch.int32 or wt.dtype != torch.float32 or tuple(idx.shape) != (T, top) or tuple(wt.shape) != (T, top):
         raise KernelError("moe_route_sort_small: idx int32 [T, top], wt float32 [T, top]")
     if not 0 < top <= min(E, MOE_MAX_TOP) or (bias is not None and bias.numel() != E):
@@ -879,9 +966,11 @@ def moe_route_sort_small(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.
     _contig("idx", idx), _contig("wt", wt)
     sq, n_partial, _, eps = _norm_args(norm_in, T)
     f = _fn("moe", "il_moe_route_sort_small", [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
-                                               _c_int, _c_int, _c_void_p, _c_int, _c_float, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p])
+                                               _c_int, _c_int, _c_void_p, _c_int, _c_float, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
+                                               _c_int, _c_float, _c_void_p])
     _check(f(_ptr(x), x.stride(0), _ptr(w), _ptr(bias), kind_of(bias.dtype) if bias is not None else 0, _ptr(z), _ptr(idx), _ptr(wt), T, H, E,
-             top, sq, n_partial, eps, _ptr(rstd_out), _ptr(group_off), _ptr(pos_of_slot), _ptr(row_of_pos), _stream()), "moe_route_sort_small")
+             top, sq, n_partial, eps, _ptr(rstd_out), _ptr(group_off), _ptr(pos_of_slot), _ptr(row_of_pos), int(extra), int(rule),
+             float(out_scale), _stream()), "moe_route_sort_small")
     count_launches(1)                             # two kernels
 
 
@@ -891,8 +980,12 @@ def route_sort_small_ok(T: int, H: int, E: int) -> bool:
     return 0 < T <= SKINNY_MAX_ROWS and H % 8 == 0 and 34 * E * 4 <= 200 * 1024
 
 
-def moe_select(z: torch.Tensor, bias: Optional[torch.Tensor], idx: torch.Tensor, wt: torch.Tensor, top: int) -> None:
-    """The choice of `moe_route` for logits a matrix product has written: z [T, E] float32 (+ bias [E]) -> idx, wt [T, top]."""
+def moe_select(z: torch.Tensor, bias: Optional[torch.Tensor], idx: torch.Tensor, wt: torch.Tensor, top: int,
+               rule: int = ROUTE_TOP_LOGITS, out_scale: float = 1.0) -> None:
+    """The choice of `moe_route` for logits a matrix product has written: z [T, E] float32 (+ bias [E]) -> idx, wt [T, top].
+    rule ROUTE_TOP_LOGITS: the `top` largest of z + bias, their weights the softmax over the chosen alone.
+    rule ROUTE_SOFTMAX_ALL: scores s = softmax(z) over all E; the `top` largest of s + bias are chosen (the lower expert wins a
+    tie); the weights are the chosen experts' s over their sum (+ 1e-20), times out_scale."""
     _need_cuda(z, bias, idx, wt)
     T, E = z.shape
     if z.dtype != torch.float32 or z.stride(1) != 1:
@@ -904,9 +997,10 @@ def moe_select(z: torch.Tensor, bias: Optional[torch.Tensor], idx: torch.Tensor,
     if bias is not None and bias.numel() != E:
         raise KernelError("moe_select: bias [E]")
     _contig("idx", idx), _contig("wt", wt)
-    f = _fn("moe", "il_moe_select", [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p])
-    _check(f(_ptr(z), z.stride(0), _ptr(bias), kind_of(bias.dtype) if bias is not None else 0, _ptr(idx), _ptr(wt), T, E, top, _stream()),
-           "moe_select")
+    f = _fn("moe", "il_moe_select", [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float,
+                                     _c_void_p])
+    _check(f(_ptr(z), z.stride(0), _ptr(bias), kind_of(bias.dtype) if bias is not None else 0, _ptr(idx), _ptr(wt), T, E, top, int(rule),
+             float(out_scale), _stream()), "moe_select")
 
 
 def moe_sort(idx: torch.Tensor, n_experts: int, group_off: torch.Tensor, pos_of_slot: torch.Tensor, row_of_pos: torch.Tensor) -> None:
@@ -933,11 +1027,21 @@ def gather_rows(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
     _check(f(_ptr(x), kind_of(x.dtype), x.stride(0), _ptr(rows), _ptr(out), n, H, _stream()), "gather_rows")
 
 
-def moe_combine(y: torch.Tensor, pos_of_slot: torch.Tensor, wt: torch.Tensor, shared_rows: Optional[torch.Tensor], out: torch.Tensor) -> None:
-    """out[t] = sum_k wt[t,k] * y[pos_of_slot[t*top + k]] (+ shared_rows[t]), summed in f32 in the order of k."""
-    _need_cuda(y, pos_of_slot, wt, shared_rows, out)
+def moe_combine(y: torch.Tensor, pos_of_slot: torch.Tensor, wt: torch.Tensor, shared_rows: Optional[torch.Tensor], out: torch.Tensor, *,
+                group_off: Optional[torch.Tensor] = None, n_real: int = 0, x: Optional[torch.Tensor] = None,
+                shared_gate: Optional[torch.Tensor] = None) -> None:
+    """out[t] = sum_k wt[t,k] * y[pos_of_slot[t*top + k]] (+ shared_rows[t]), summed in f32 in the order of k.
+    With `group_off` (int32, the sorted order's group starts), `n_real` and `x` [T, H]: the experts from n_real on have no
+    weights and return their input - a choice whose place is group_off[n_real] or later adds wt * x[t] instead of a row of y.
+    `shared_gate`: float32 [T] (any stride) - the shared row is multiplied by its sigmoid."""
+    _need_cuda(y, pos_of_slot, wt, shared_rows, out, group_off, x, shared_gate)
     T, top = wt.shape
     H = out.shape[1]
+    if group_off is not None and (x is None or x.dtype != out.dtype or tuple(x.shape) != (T, H) or x.stride(1) != 1
+                                  or group_off.dtype != torch.int32 or group_off.numel() <= n_real):
+        raise KernelError("moe_combine: identity experts need group_off int32 [> n_real] and x [T, H] of out's dtype")
+    if shared_gate is not None and (shared_gate.dtype != torch.float32 or shared_gate.dim() != 1 or shared_gate.numel() != T):
+        raise KernelError("moe_combine: shared_gate float32 [T]")
     if y.dtype != out.dtype or y.shape[1] != H or out.shape[0] != T or y.shape[0] < T * top:
         raise KernelError("moe_combine: y [T * top, H], out [T, H] of the same dtype")
     if shared_rows is not None and (shared_rows.dtype != out.dtype or tuple(shared_rows.shape) != (T, H)):
@@ -945,8 +1049,11 @@ def moe_combine(y: torch.Tensor, pos_of_slot: torch.Tensor, wt: torch.Tensor, sh
     _contig("y", y), _contig("out", out), _contig("wt", wt)
     if shared_rows is not None:
         _contig("shared_rows", shared_rows)
-    f = _fn("moe", "il_moe_combine", [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p])
-    _check(f(_ptr(y), kind_of(y.dtype), _ptr(pos_of_slot), _ptr(wt), _ptr(shared_rows), _ptr(out), T, H, top, _stream()), "moe_combine")
+    f = _fn("moe", "il_moe_combine", [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int,
+                                      _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p])
+    _check(f(_ptr(y), kind_of(y.dtype), _ptr(pos_of_slot), _ptr(wt), _ptr(shared_rows), _ptr(out), T, H, top, _ptr(group_off), int(n_real),
+             _ptr(x), 0 if x is None else x.stride(0), _ptr(shared_gate), 0 if shared_gate is None else shared_gate.stride(0), _stream()),
+           "moe_combine")
 
 
 def moe_combine_resid(y: torch.Tensor, pos_of_slot: torch.Tensor, wt: torch.Tensor, shared_rows: Optional[torch.Tensor], resid: torch.Tensor,
@@ -1137,7 +1244,7 @@ def delta_prep(qk: torch.Tensor, q_off: int, k_off: int, n_qk_heads: int, dim: i
              _ptr(a_log), _ptr(dt_bias), _ptr(beta), _ptr(gdec), n_heads, T, _stream()), "delta_prep")
 
 
-SCAN_DECAY, SCAN_DELTA, SCAN_GATED = 0, 1, 3
+SCAN_DECAY, SCAN_DELTA, SCAN_GATED, SCAN_CHANNEL_DECAY = 0, 1, 3, 4
 
 
 def matrix_state_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, n_heads: int, n_qk_heads: int, dim: int,
@@ -1149,6 +1256,8 @@ def matrix_state_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tens
     SCAN_DECAY: S = decay[h] S + k v^T, o = S^T q. SCAN_DELTA: S = g S; u = beta (v - S^T k); S += k u^T; o = S^T q.
     SCAN_GATED: S = g S + beta k [v, 1]^T, o = S^T q with g, beta per token and head (`gdec`, `beta`); the state and the output
     have one column more than v (`vdim` counts it: v heads are vdim - 1 wide), fed by the constant 1.
+    SCAN_CHANNEL_DECAY: o = (S + diag(u_h) k v^T)^T q, then S = diag(w_t) S + k v^T: `gdec` holds w, float32 [T, >= heads*dim]
+    (a decay per token, head and key channel; a view with a row stride), `decay` the bonus u, float32 [heads, dim].
     q, k float32 [T, >= n_qk_heads*dim] (views with a row stride), v float32 [T, >= n_heads*vdim], out float32 [T, n_heads*vdim];
     value head h reads q/k head h // (n_heads // n_qk_heads). in_act 1: silu on q, k, v as read.
     state float32 [slots, n_heads, vdim, dim] (S column by column: the dim entries behind one output lie together). `generic`: the kernel that keeps the state in shared memory (any size; the
@@ -1167,6 +1276,12 @@ def matrix_state_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tens
     v_cols = n_heads * (vdim - 1 if mode == SCAN_GATED else vdim)
     if out.shape[1] != n_heads * vdim or q.shape[1] < n_qk_heads * dim or k.shape[1] < n_qk_heads * dim or v.shape[1] < v_cols:
         raise KernelError("matrix_state_scan: shapes")
+    ld_g = 0
+    if mode == SCAN_CHANNEL_DECAY:
+        if (gdec is None or decay is None or gdec.dtype != torch.float32 or gdec.stride(-1) != 1 or gdec.shape[1] < n_heads * dim
+                or decay.dtype != torch.float32 or not decay.is_contiguous() or decay.numel() != n_heads * dim or n_qk_heads != n_heads):
+            raise KernelError("matrix_state_scan: channel decays float32 [T, heads*dim], bonus float32 [heads, dim], as many q/k heads as heads")
+        ld_g = gdec.stride(0)
     if seg_len > 0:
         _need_cuda(seg_state)
         if (mode != SCAN_DECAY or generic or single or dim > 256 or seg_len % 8 or n_tiles <= 0 or seg_state is None
@@ -1179,7 +1294,7 @@ def matrix_state_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tens
     _check(f(mode, _ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), v.stride(0), n_heads, n_qk_heads, dim, vdim, in_act,
              _ptr(decay), _ptr(beta), _ptr(gdec), _ptr(state), state.stride(0), _ptr(read_slots), _ptr(write_slots),
              _ptr(entry_qstart), n_entries, _ptr(out), out.stride(0), int(generic), first_entry, int(single), seg_len, n_tiles,
-             _ptr(seg_state), _stream()), "matrix_state_scan")
+             _ptr(seg_state), ld_g, _stream()), "matrix_state_scan")
     if seg_len > 0:
         count_launches(1)                         # the second pass
 
@@ -1203,6 +1318,48 @@ def matrix_state_scan_step(ctx, *args, **kw) -> None:
 
 
 SCAN_SEGMENT = 128
+
+
+def token_shift_mix(h: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, read_slots: torch.Tensor, write_slots: Optional[torch.Tensor],
+                    tok_entry: torch.Tensor, entry_qstart: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, m*W + c] = h[t, c] + (h_prev[t, c] - h[t, c]) * mu[m, c]: the blends of a token's row with the row before it in its
+    sequence, one per row of `mu` (float32 [n_mix, W]). The row before a step's first token is the request's state (float32
+    [slots, W]; the zero slot for a sequence's first token), which receives the entry's last row (`write_slots` None: not)."""
+    _need_cuda(h, mu, state, read_slots, write_slots, tok_entry, entry_qstart, out)
+    _i32("token_shift_mix", read_slots, tok_entry, entry_qstart)
+    T, W = h.shape
+    n_mix = mu.shape[0]
+    if mu.dtype != torch.float32 or not mu.is_contiguous() or mu.shape[1] != W or h.stride(1) != 1:
+        raise KernelError("token_shift_mix: mu float32 [n_mix, W], h [T, W] with contiguous rows")
+    if out.dtype != h.dtype or tuple(out.shape) != (T, n_mix * W) or out.stride(1) != 1:
+        raise KernelError("token_shift_mix: out [T, n_mix * W] of h's dtype")
+    if state.dtype != torch.float32 or not state.is_contiguous() or state.dim() != 2 or state.shape[1] != W:
+        raise KernelError("token_shift_mix: state float32 [slots, W]")
+    f = _fn("seqmix", "il_token_shift_mix", [_c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_ll, _c_void_p, _c_void_p, _c_void_p,
+                                             _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p])
+    _check(f(_ptr(h), kind_of(h.dtype), h.stride(0), _ptr(mu), n_mix, _ptr(state), state.stride(0), _ptr(read_slots), _ptr(write_slots),
+             _ptr(tok_entry), _ptr(entry_qstart), _ptr(out), out.stride(0), W, T, _stream()), "token_shift_mix")
+
+
+def double_exp_decay(z: torch.Tensor, w0: Optional[torch.Tensor], cols: int) -> None:
+    """z[:, :cols] = exp(-exp(z[:, :cols] + w0)) in place: float32 rows, w0 float32 [cols] or None."""
+    _need_cuda(z, w0)
+    if z.dtype != torch.float32 or z.dim() != 2 or z.stride(1) != 1 or cols > z.shape[1]:
+        raise KernelError("double_exp_decay: float32 [T, >= cols] with contiguous rows")
+    if w0 is not None and (w0.dtype != torch.float32 or w0.numel() != cols or not w0.is_contiguous()):
+        raise KernelError("double_exp_decay: w0 float32 [cols]")
+    f = _fn("seqmix", "il_double_exp_decay", [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p])
+    _check(f(_ptr(z), z.stride(0), _ptr(w0), cols, z.shape[0], _stream()), "double_exp_decay")
+
+
+def tanh_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = tanh(x): x contiguous float32, out contiguous float32 or bfloat16 of the same shape."""
+    _need_cuda(x, out)
+    if x.dtype != torch.float32 or x.shape != out.shape:
+        raise KernelError("tanh_rows: float32 in, one shape")
+    _contig("x", x), _contig("out", out)
+    f = _fn("seqmix", "il_tanh_rows", [_c_void_p, _c_void_p, _c_int, _c_ll, _c_void_p])
+    _check(f(_ptr(x), _ptr(out), kind_of(out.dtype), x.numel(), _stream()), "tanh_rows")
 
 
 def silu_cols(x: torch.Tensor, cols: int) -> None:

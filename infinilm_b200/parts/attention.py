@@ -28,7 +28,10 @@ class PagedAttend:
     `shared_kv`: the mixer writes the same vector to the K and the V plane (one latent that is key and value); the decode
     kernel then reads the K plane alone. The prompt kernels, bound by arithmetic, read both planes as they lie.
     `dist_bias`: float32 [far + 1, heads] on the device or None - a bias by distance, added to the scaled score of a key n
-    positions back as dist_bias[min(n, far), head] (constant from `far` on)."""
+    positions back as dist_bias[min(n, far), head] (constant from `far` on).
+    `chunk`: instead of a sliding window, runs of `chunk` positions counted from position 0 of the sequence; a query sees the
+    keys of its own run up to itself (the kernels take it as a negative window). The cache keeps every page: a window's
+    pages are given back behind it, a chunked layer's are not (another layer may read them)."""
 
     # The fast bfloat16 kernels take kernel pages of 16 keys (the cache manager lays larger pages out as runs of them)
     # and at most 64 query heads per kv head; anything else, and the whole float32 path, runs the plain kernel.
@@ -39,8 +42,13 @@ class PagedAttend:
     WAVE_FILL = 2.0 / 3.0                         # share of the blocks the device holds at once that the splits aim at
 
     def __init__(self, dtype, n_heads: int, n_kv_heads: int, head_dim: int, scale: float, window: Optional[int] = None,
-                 force_plain: bool = False, prefill_kernel: str = "auto", shared_kv: bool = False):
+                 force_plain: bool = False, prefill_kernel: str = "auto", shared_kv: bool = False, chunk: Optional[int] = None):
+        if chunk is not None and (window is not None or int(chunk) < 1):
+            raise ValueError("attention: a mask is a window or runs of a positive size, not both")
         self.dtype, self.nh, self.nkv, self.hd, self.scale, self.window = dtype, n_heads, n_kv_heads, head_dim, scale, window
+        self.chunk = None if chunk is None else int(chunk)
+        self.span = self.chunk if self.chunk is not None else window          # the most keys a query sees (None: all)
+        self.mask_arg = -self.chunk if self.chunk is not None else window     # what the kernels take
         self.force_plain, self.prefill_kernel, self.shared_kv = force_plain, prefill_kernel, shared_kv
         self.sink: Optional[torch.Tensor] = None
         self.dist_bias: Optional[torch.Tensor] = None
@@ -66,20 +74,20 @@ class PagedAttend:
                               "head sizes in steps of 16 up to 256): the plain kernel runs, at a fraction of their speed",
                               RuntimeWarning, stacklevel=2)
             ops.attention_plain(qkv, out, cache.storage, cache.block_table, ctx.tok_pos, ctx.tok_entry,
-                                cache.page_size, self.nh, self.nkv, self.hd, self.scale, self.window, self.sink, self.dist_bias)
+                                cache.page_size, self.nh, self.nkv, self.hd, self.scale, self.mask_arg, self.sink, self.dist_bias)
             return
         n_dec, E = ctx.n_decode, ctx.n_entries
         if n_dec > 0:
             max_len = max(ctx.h_kvlen[:n_dec])
-            if self.window is not None:
-                max_len = min(max_len, self.window + self.FAST_PAGE)
-            max_pages = (max_len + self.FAST_PAGE - 1) // self.FAST_PAGE + (1 if self.window is not None else 0)
+            if self.span is not None:
+                max_len = min(max_len, self.span + self.FAST_PAGE)
+            max_pages = (max_len + self.FAST_PAGE - 1) // self.FAST_PAGE + (1 if self.span is not None else 0)
             base = n_dec * self.nkv * ((G + 15) // 16)
             v_is_k = self.shared_kv and cache.tma_map is not None
             n_splits = self.decode_splits(base, max_pages, ops.attention_decode_resident_blocks(self.hd, v_is_k))
             rows = n_dec * self.nh * n_splits
             ops.attention_decode(qkv, out, cache.storage, cache.block_table, ctx.entry_kvlen, n_dec, cache.page_size,
-                                 self.nh, self.nkv, self.hd, self.scale, self.window, 0, n_splits,
+                                 self.nh, self.nkv, self.hd, self.scale, self.mask_arg, 0, n_splits,
                                  ctx.ws.flat("attn_o_part", rows * self.hd, torch.float32),
                                  ctx.ws.flat("attn_ml_part", rows * 2, torch.float32), kv_map=cache.tma_map, sink=self.sink,
                                  v_is_k=v_is_k, dist_bias=self.dist_bias)
@@ -93,11 +101,11 @@ class PagedAttend:
             if tc5:
                 ops.attention_prefill_tc5(qkv, out, cache.tma_map, cache.block_table, ctx.entry_qstart, ctx.entry_kvlen,
                                           n_dec, E, n_tiles, cache.page_size, self.nh, self.nkv, self.hd, self.scale,
-                                          self.window, sink=self.sink, dist_bias=self.dist_bias)
+                                          self.mask_arg, sink=self.sink, dist_bias=self.dist_bias)
             else:
                 ops.attention_prefill(qkv, out, cache.storage, cache.block_table, ctx.entry_qstart, ctx.entry_kvlen,
                                       n_dec, E, n_tiles, cache.page_size, self.nh, self.nkv, self.hd, self.scale,
-                                      self.window, sink=self.sink, dist_bias=self.dist_bias)
+                                      self.mask_arg, sink=self.sink, dist_bias=self.dist_bias)
 
 
 class Attention(Mixer):

@@ -138,6 +138,8 @@ class Arrangement:
 
     takes_pre_add = False                        # True: `run` has the `pre_add` argument
 
+    takes_next_block = False                     # True: `run` has the argument `next_block=None`, the block that runs next (or None)
+
     takes_next_norm = False                      # True: `run` has the `next_norm` argument and may use it
 
     def accepts_normed_input(self, T: int) -> bool:

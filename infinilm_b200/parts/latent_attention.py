@@ -7,6 +7,8 @@ Per token (h its normed input, H heads, d query/key dimensions and e value dimen
     p   = softmax over the keys i <= t of (q_j . k_j) * scale, with exp(sink_j) in the denominator besides
     y   = W_o (concat_j(sum_i p_i v_j,i) * sigmoid(W_g h))
 
+(`q_rank` None: no query latent, q = W_q h.)
+
 The cache holds c alone, so the products with W_uk and W_uv are moved to the query side, which changes no value:
     q_j . (W_uk[j] c) = (W_uk[j]^T q_j) . c                      a query of width r against the latents themselves
     sum_i p_i W_uv[j] c_i = W_uv[j] (sum_i p_i c_i)              the weighted latent, up-projected once per query
@@ -28,7 +30,8 @@ from .spec import CacheNeed, WeightSpec
 
 
 class LatentAttention(Mixer):
-    """params: hidden, n_heads, qk_dim, v_dim, q_rank, kv_rank, scale, eps (of the two latent norms), sink (a learned
+    """params: hidden, n_heads, qk_dim, v_dim, q_rank (None: the queries are projected from the input directly, tensor `q`
+    instead of `dq`, `dq.norm`, `uq`), kv_rank, scale, eps (of the two latent norms), sink (a learned
     number per head in the softmax's denominator), gate (heads multiplied by sigmoid(W_g h)), window (None: all keys)."""
     graph_safe = True
     # From this many rows on, the bfloat16 path hands the two per-head products to the library's batched product (written
@@ -42,17 +45,19 @@ class LatentAttention(Mixer):
         p = params
         self.hidden, self.nh = int(p["hidden"]), int(p["n_heads"])
         self.d, self.e = int(p["qk_dim"]), int(p["v_dim"])
-        self.qr, self.r = int(p["q_rank"]), int(p["kv_rank"])
+        self.direct_q = p.get("q_rank") is None
+        self.qr, self.r = (0 if self.direct_q else int(p["q_rank"])), int(p["kv_rank"])
         self.scale, self.eps = float(p["scale"]), float(p["eps"])
         self.has_sink, self.has_gate = bool(p.get("sink", True)), bool(p.get("gate", True))
         self.window: Optional[int] = p.get("window")
-        if min(self.hidden, self.nh, self.d, self.e, self.qr, self.r) <= 0:
+        if min(self.hidden, self.nh, self.d, self.e, self.r) <= 0 or (self.qr <= 0 and not self.direct_q):
             raise ValueError("latent attention: sizes must be positive")
         if self.r > 1024:
             raise ValueError(f"latent attention: a latent of width {self.r} is beyond the attention kernels (1024; the fast ones end at 256)")
-        self.n_down = self.qr + self.r + (self.nh * self.e if self.has_gate else 0)
-        self.down = Linear(self.hidden, self.n_down, dtype)          # rows: query latent | key/value latent | gate
-        self.up_q = Linear(self.qr, self.nh * self.d, dtype)
+        self.n_q = self.nh * self.d if self.direct_q else self.qr     # the first columns of the joint product: the queries, or their latent
+        self.n_down = self.n_q + self.r + (self.nh * self.e if self.has_gate else 0)
+        self.down = Linear(self.hidden, self.n_down, dtype)          # rows: query latent (or queries) | key/value latent | gate
+        self.up_q = None if self.direct_q else Linear(self.qr, self.nh * self.d, dtype)
         self.out = Linear(self.nh * self.e, self.hidden, dtype)
         self.core = PagedAttend(dtype, self.nh, 1, self.r, self.scale, self.window,
                                 force_plain=bool(p.get("plain_kernel", False)), prefill_kernel=str(p.get("prefill_kernel", "auto")),
@@ -60,9 +65,10 @@ class LatentAttention(Mixer):
 
     def weight_specs(self) -> List[WeightSpec]:
         H, W = self.nh, self.hidden
-        specs = [WeightSpec("dq", (self.qr, W)), WeightSpec("dq.norm", (self.qr,), "vector", ("ones_normal", 0.05)),
-                 WeightSpec("uq", (H * self.d, self.qr), init=("normal", 0.08)),
-                 WeightSpec("dkv", (self.r, W)), WeightSpec("dkv.norm", (self.r,), "vector", ("ones_normal", 0.05)),
+        specs = [WeightSpec("q", (H * self.d, W))] if self.direct_q else [
+            WeightSpec("dq", (self.qr, W)), WeightSpec("dq.norm", (self.qr,), "vector", ("ones_normal", 0.05)),
+            WeightSpec("uq", (H * self.d, self.qr), init=("normal", 0.08))]
+        specs += [WeightSpec("dkv", (self.r, W)), WeightSpec("dkv.norm", (self.r,), "vector", ("ones_normal", 0.05)),
                  WeightSpec("uk", (H * self.d, self.r), init=("normal", 0.08)), WeightSpec("uv", (H * self.e, self.r), init=("normal", 0.08)),
                  WeightSpec("o", (W, H * self.e))]
         if self.has_sink:
@@ -73,15 +79,16 @@ class LatentAttention(Mixer):
 
     def set_weights(self, t: Dict[str, torch.Tensor]) -> None:
         H = self.nh
-        self.down.set(torch.cat([t["dq"], t["dkv"]] + ([t["g"]] if self.has_gate else []), dim=0))
-        self.up_q.set(t["uq"])
+        self.down.set(torch.cat([t["q" if self.direct_q else "dq"], t["dkv"]] + ([t["g"]] if self.has_gate else []), dim=0))
+        if not self.direct_q:
+            self.up_q.set(t["uq"])
         self.out.set(t["o"])
         # W_uk[j]^T as [H, r, d]: the product that turns a head's query into a query against the latents
         self.uk_t = t["uk"].to(self.dtype).view(H, self.d, self.r).transpose(1, 2).contiguous()
         self.uv = t["uv"].to(self.dtype).view(H, self.e, self.r).contiguous()
         self._uk_t_kn, self._uv_kn = self.uk_t.transpose(1, 2), self.uv.transpose(1, 2)      # [H, K, N] views for the library's batched product
-        vec = torch.float32 if self.dtype == torch.float32 else t["dq.norm"].dtype
-        self.nq, self.nkv = t["dq.norm"].to(vec).contiguous(), t["dkv.norm"].to(vec).contiguous()
+        vec = torch.float32 if self.dtype == torch.float32 else t["dkv.norm"].dtype
+        self.nq, self.nkv = (None if self.direct_q else t["dq.norm"].to(vec).contiguous()), t["dkv.norm"].to(vec).contiguous()
         self.core.sink = t["sink"].to(torch.float32).contiguous() if self.has_sink else None
 
     def cache_need(self) -> Optional[CacheNeed]:
@@ -101,10 +108,10 @@ class LatentAttention(Mixer):
             ops.gemm_skinny(x.xw, self.down.weight, proj, self.down.alpha, self.down.bias, norm_in=x)
         else:
             proj = self.down(x, ws.rows("lat_down", T, self.n_down, dt))
-        cq = ws.rows("lat_cq", T, self.qr, dt)
-        ops.latent_norm_store(proj, 0, self.qr, self.qr, self.r, self.nq, self.nkv, self.eps, cq, None, ctx.tok_pos, ctx.tok_entry,
+        cq = None if self.direct_q else ws.rows("lat_cq", T, self.qr, dt)
+        ops.latent_norm_store(proj, 0, self.qr, self.n_q, self.r, self.nq, self.nkv, self.eps, cq, None, ctx.tok_pos, ctx.tok_entry,
                               cache.block_table, cache.storage if cache.writable else None, cache.page_size)
-        q = self.up_q(cq, ws.rows("lat_q", T, H * self.d, dt))
+        q = proj[:, :self.n_q] if self.direct_q else self.up_q(cq, ws.rows("lat_q", T, H * self.d, dt))
         library = dt == torch.bfloat16 and T >= self.LIBRARY_FROM_ROWS and not bool(self.params.get("own_products_only", False))
         q_lat = ws.rows("lat_qlat", T, H * self.r, dt)
         if library:
@@ -114,7 +121,7 @@ class LatentAttention(Mixer):
         o_lat = ws.rows("lat_olat", T, H * self.r, dt)
         self.core.run(q_lat, o_lat, ctx, cache)
         o = ws.rows("lat_o", T, H * self.e, dt)
-        gate = proj[:, self.qr + self.r:] if self.has_gate else None
+        gate = proj[:, self.n_q + self.r:] if self.has_gate else None
         if library:
             torch.bmm(o_lat.view(T, H, self.r).transpose(0, 1), self._uv_kn, out=o.view(T, H, self.e).transpose(0, 1))
             if gate is not None:

@@ -14,6 +14,12 @@ MatrixLSTM (the matrix memory of an xLSTM block, with exponential gates kept in 
     m_t = max(f + m_(t-1), i);  S_t = exp(f + m_(t-1) - m_t) S_(t-1) + exp(i - m_t) k v^T;  n_t the same with k alone
     o = S_t^T q / (max(|n_t . q|, exp(-m_t)) + 1e-6);  y = W_o ( rms_norm(o per head) * w * sigmoid(W_g h) )
     (S, n and m start at zero; the state is S with n as one more column, and m)
+ChannelDecayMixer (time mixing in the manner of RWKV's later versions: a decay per head and key channel that depends on the token):
+    every projection reads its own blend of the token's input and its predecessor's, x_s = h + (h_prev - h) * mu_s, s in r, k, v, g, w
+    r, k, v = W_r x_r, W_k x_k, W_v x_v (heads x dim);  gate = silu(W_g x_g);  w = exp(-exp(w0 + W_w2 tanh(W_w1 x_w)))
+    per head  o_t = (S_(t-1) + diag(u) k_t v_t^T)^T r_t;  S_t = diag(w_t) S_(t-1) + k_t v_t^T      (u: a bonus for the token itself)
+    y = W_o ( rms_norm(o per head) * w_norm * gate )
+    (S starts at zero; the state is S and the last token's h)
 The projections leave float32 on both paths (what enters a recurrence, its gates and decays stay 32-bit).
 """
 from __future__ import annotations
@@ -238,6 +244,84 @@ class MatrixLSTM(Mixer):
         return self.o_proj(gated, ctx.ws.rows("mlstm_branch", T, self.hidden, self.dtype))
 
 
+class ChannelDecayMixer(Mixer):
+    """params: hidden, n_heads, dim (key, value and receptance size of a head), decay_rank (rows of w1; None: the stored tensor's),
+    eps (of the output norm).
+    Tensors: mu.r, mu.k, mu.v, mu.g, mu.w [hidden]; r, k, v, g [heads * dim, hidden]; w1 [rank, hidden], w2 [heads * dim, rank],
+    w0 [heads * dim]; u [heads, dim]; norm [heads * dim]; o [hidden, heads * dim]."""
+    graph_safe = True
+    MIXES = ("r", "k", "v", "g", "w")
+
+    def __init__(self, params, prefix, dtype):
+        super().__init__(params, prefix, dtype)
+        p = params
+        self.hidden, self.nh, self.d = int(p["hidden"]), int(p["n_heads"]), int(p["dim"])
+        if min(self.hidden, self.nh, self.d) <= 0:
+            raise ValueError("channel-decay mixer: sizes must be positive")
+        self.rank = None if p.get("decay_rank") is None else int(p["decay_rank"])
+        self.eps = float(p["eps"])
+        self.n = self.nh * self.d
+        self.rkv = [Linear(self.hidden, self.n, dtype) for _ in range(3)]
+        self.g_proj = Linear(self.hidden, self.n, dtype)
+        self.o_proj = Linear(self.n, self.hidden, dtype)
+        self.w1 = self.w2 = self.mu = self.u = self.norm_w = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        H, n = self.hidden, self.n
+        r = -1 if self.rank is None else self.rank
+        return ([WeightSpec("mu." + m, (H,), "vector", ("normal", 0.3)) for m in self.MIXES]
+                + [WeightSpec(x, (n, H)) for x in ("r", "k", "v", "g")]
+                + [WeightSpec("w1", (r, H), free=16), WeightSpec("w2", (n, r), init=("normal", 0.1), free=16),
+                   WeightSpec("w0", (n,), "vector", ("normal", 0.5)), WeightSpec("u", (self.nh, self.d), "vector", ("normal", 0.5)),
+                   WeightSpec("norm", (n,), "vector", ("ones_normal", 0.05)), WeightSpec("o", (H, n))])
+
+    def set_weights(self, t: Dict[str, torch.Tensor]) -> None:
+        for lin, name in zip(self.rkv, ("r", "k", "v")):
+            lin.set(t[name])
+        self.g_proj.set(t["g"])
+        self.o_proj.set(t["o"])
+        rank = int(t["w1"].shape[0])
+        if tuple(t["w2"].shape) != (self.n, rank):
+            raise ValueError(f"channel-decay mixer: w2 {tuple(t['w2'].shape)} does not follow w1's {rank} rows")
+        self.w1, self.w2 = Linear(self.hidden, rank, self.dtype), Linear(rank, self.n, self.dtype)
+        self.w1.set(t["w1"])
+        self.w2.set(t["w2"], t["w0"].to(torch.float32))          # w0 joins the product as its bias, in float32
+        self.mu = torch.stack([t["mu." + m].to(torch.float32) for m in self.MIXES]).contiguous()
+        self.u = t["u"].to(torch.float32).contiguous()
+        self.norm_w = t["norm"].to(torch.float32).contiguous()
+
+    def cache_need(self):
+        # S [heads, dim, dim] (column by column) and the last token's input row
+        return (CacheNeed("state", shape=(self.nh, self.d, self.d), dtype="float32"),
+                CacheNeed("state", shape=(self.hidden,), dtype="float32"))
+
+    def forward(self, x, ctx, cache):
+        S, prev = cache
+        T, W, n, dt = x.shape[0], self.hidden, self.n, self.dtype
+        ws = ctx.ws
+        mix = ws.rows("cdm_mix", T, len(self.MIXES) * W, dt)
+        ops.token_shift_mix(x, self.mu, prev.storage, prev.read_slots, prev.write_slots if prev.writable else None, ctx.tok_entry,
+                            ctx.entry_qstart, mix)
+        rkv = ws.rows("cdm_rkv", T, 3 * n, torch.float32)
+        for i, lin in enumerate(self.rkv):
+            lin(mix[:, i * W:(i + 1) * W], rkv[:, i * n:(i + 1) * n], out_f32=True)
+        gate = self.g_proj(mix[:, 3 * W:4 * W], ws.rows("cdm_gate", T, n, dt))
+        rank = self.w1.out_features
+        low = self.w1(mix[:, 4 * W:5 * W], ws.rows("cdm_low", T, rank, torch.float32), out_f32=True)
+        low_t = ws.rows("cdm_low_t", T, rank, dt)
+        ops.tanh_rows(low, low_t)
+        decay = self.w2(low_t, ws.rows("cdm_decay", T, n, torch.float32), out_f32=True)
+        ops.double_exp_decay(decay, None, n)
+        o = ws.rows("cdm_o", T, n, torch.float32)
+        ops.matrix_state_scan_step(ctx, ops.SCAN_CHANNEL_DECAY, rkv[:, :n], rkv[:, n:2 * n], rkv[:, 2 * n:], self.nh, self.nh, self.d, self.d, 0,
+                                   self.u, None, decay, S.storage, S.read_slots, S.write_slots if S.writable else S.read_slots,
+                                   ctx.entry_qstart, out=o)
+        gated = ws.rows("cdm_gated", T, n, dt)
+        ops.group_norm_gate(o, self.norm_w, self.eps, gate, 0, ops.GATE_SILU, gated, self.d)
+        return self.o_proj(gated, ws.rows("cdm_branch", T, self.hidden, dt))
+
+
 register_part("mixer", "decay_linear_attention", DecayLinearAttention)
+register_part("mixer", "channel_decay", ChannelDecayMixer)
 register_part("mixer", "matrix_lstm", MatrixLSTM)
 register_part("mixer", "gated_delta_rule", GatedDeltaRule)

@@ -1,5 +1,8 @@
-"""Softmax attention over the paged cache whose queries and keys are normed per head and whose positions rotate nothing:
-they enter, if at all, as a learned bias by distance on the scores or as a temperature on the queries.
+"""Softmax attention over the paged cache whose queries and keys are normed. In its first form the norm is per head and
+positions rotate nothing: they enter, if at all, as a learned bias by distance on the scores or as a temperature on the
+queries. In its second form (`norm_over` "projection") the norm runs over a token's whole query projection (all heads at
+once; the keys' likewise) with a weight of that many entries, a rotary encoding (`position`) may turn part of every head
+afterwards, and the mask may be runs of `chunk` positions or a sliding `window`.
 
     [q | k | v | g] = W h (+ b)
     q_h <- rms_norm(q_h) * w_q * temp(pos),  k_g <- rms_norm(k_g) * w_k        (one weight vector each, shared by the heads)
@@ -26,9 +29,9 @@ import torch
 
 from .. import ops
 from .attention import PagedAttend
-from .base import Mixer, register_part
+from .base import Mixer, build_part, register_part
 from .linear import Linear
-from .spec import CacheNeed, WeightSpec
+from .spec import CacheNeed, PartSpec, WeightSpec
 
 
 def distance_buckets(rows: int, far: int) -> List[int]:
@@ -49,7 +52,10 @@ class QKNormAttention(Mixer):
     """params: hidden, n_heads, n_kv_heads, qk_dim, v_dim, scale, eps (of the query and key norms), qkv_bias,
     value_from_key (the values are the un-normed keys), own_kv (False: the run order gives this entry another entry's cache),
     distance_bias (None or {"rows": B or None - the table's own row count -, "far": D}), q_temperature (None or {"coef": c, "every": n}), sink_zero (a key without
-    a value and with score 0 joins the softmax), output_gate, plain_kernel, prefill_kernel."""
+    a value and with score 0 joins the softmax), output_gate, plain_kernel, prefill_kernel;
+    norm_over ("head", the default, or "projection": q.norm has heads * qk_dim entries, k.norm kv_heads * qk_dim),
+    position (PartSpec of a rotary encoding, with norm_over "projection"), chunk (runs of that many positions, counted from the
+    sequence's start; a query sees its own run) or window (a sliding window; its pages are given back behind it)."""
     graph_safe = True
 
     def __init__(self, params, prefix, dtype):
@@ -77,6 +83,15 @@ class QKNormAttention(Mixer):
         if qt and self.t_every < 1:
             raise ValueError("attention: the query temperature's step must be at least 1")
         self.sink_zero = bool(p.get("sink_zero", False))
+        self.norm_rows = str(p.get("norm_over", "head")) == "projection"
+        if str(p.get("norm_over", "head")) not in ("head", "projection"):
+            raise ValueError("attention: norm_over is 'head' or 'projection'")
+        self.position = build_part("position", p.get("position") or PartSpec("none"), dtype)
+        if self.position.has_transform or (self.position.rot_dim and not self.norm_rows) or self.position.rot_dim > self.dk:
+            raise ValueError("attention: a rotary table of at most qk_dim dimensions, with the norm over the projection")
+        if self.norm_rows and (self.v_from_k or qt):
+            raise ValueError("attention: the norm over the projection goes with values of their own and no query temperature")
+        self.window, self.chunk = p.get("window"), p.get("chunk")
         # the projection's columns: [q | k | v | g], k and v only with a cache of its own, v only if it is not k
         self.nq, self.nk, self.nvv = self.nh * self.dk, self.nkv * self.dk, self.nkv * self.dv
         self.q_off, off = 0, self.nq
@@ -92,18 +107,18 @@ class QKNormAttention(Mixer):
         self.n_proj_pad = (self.n_proj + 7) // 8 * 8
         self.proj = Linear(self.hidden, self.n_proj_pad, dtype)
         self.o_proj = Linear(self.nh * self.dv, self.hidden, dtype)
-        self.core = PagedAttend(dtype, self.nh, self.nkv, self.hd, self.scale, None, bool(p.get("plain_kernel", False)),
-                                str(p.get("prefill_kernel", "auto")))
+        self.core = PagedAttend(dtype, self.nh, self.nkv, self.hd, self.scale, self.window, bool(p.get("plain_kernel", False)),
+                                str(p.get("prefill_kernel", "auto")), chunk=self.chunk)
         self.w_q = self.w_k = None
 
     def weight_specs(self) -> List[WeightSpec]:
         H = self.hidden
         specs = [WeightSpec("q", (self.nq, H)), WeightSpec("o", (H, self.nh * self.dv)),
-                 WeightSpec("q.norm", (self.dk,), "vector", ("ones_normal", 0.05))]
+                 WeightSpec("q.norm", (self.nq if self.norm_rows else self.dk,), "vector", ("ones_normal", 0.05))]
         if self.qkv_bias:
             specs.append(WeightSpec("q.b", (self.nq,), "vector", ("normal", 0.02)))
         if self.own_kv:
-            specs += [WeightSpec("k", (self.nk, H)), WeightSpec("k.norm", (self.dk,), "vector", ("ones_normal", 0.05))]
+            specs += [WeightSpec("k", (self.nk, H)), WeightSpec("k.norm", (self.nk if self.norm_rows else self.dk,), "vector", ("ones_normal", 0.05))]
             if self.qkv_bias:
                 specs.append(WeightSpec("k.b", (self.nk,), "vector", ("normal", 0.02)))
             if not self.v_from_k:
@@ -136,10 +151,11 @@ class QKNormAttention(Mixer):
             self.core.dist_bias = t["rel"].to(torch.float32)[idx].contiguous()          # [far + 1, heads]
         if self.sink_zero:
             self.core.sink = torch.zeros(self.nh, dtype=torch.float32, device=dev)
+        self.position.to_device(dev)
 
     def cache_need(self) -> Optional[CacheNeed]:
         # (an entry that reads another's cache is never asked: the run order names the owner)
-        return CacheNeed("paged_kv", n_kv_heads=self.nkv, head_dim=self.hd, window=None)
+        return CacheNeed("paged_kv", n_kv_heads=self.nkv, head_dim=self.hd, window=self.window)
 
     def forward(self, x, ctx, cache):
         T, hd = x.shape[0], self.hd
@@ -147,9 +163,14 @@ class QKNormAttention(Mixer):
             raise ValueError("attention: a mixer with keys of its own writes its cache; one without reads another entry's")
         proj = self.proj(x, ctx.ws.rows("qna_proj", T, self.n_proj_pad, self.dtype))
         q = ctx.ws.rows("qna_q", T, self.nh * hd, self.dtype)
-        ops.qk_norm_store(proj, self.q_off, self.k_off, self.v_off if self.own_kv else 0, self.nh, self.nkv, self.dk, self.dv, hd,
-                          self.w_q, self.w_k, self.eps, self.t_coef, self.t_every, q, ctx.tok_pos, ctx.tok_entry, cache.block_table,
-                          cache.storage if self.own_kv else None, cache.page_size)
+        if self.norm_rows:
+            ops.qk_rows_norm_rope_store(proj, self.q_off, self.k_off, self.v_off if self.own_kv else 0, self.nh, self.nkv, self.dk, self.dv, hd,
+                                        self.w_q, self.w_k, self.eps, self.position.rot_dim, self.position.inv_freq, q, ctx.tok_pos,
+                                        ctx.tok_entry, cache.block_table, cache.storage if self.own_kv else None, cache.page_size)
+        else:
+            ops.qk_norm_store(proj, self.q_off, self.k_off, self.v_off if self.own_kv else 0, self.nh, self.nkv, self.dk, self.dv, hd,
+                              self.w_q, self.w_k, self.eps, self.t_coef, self.t_every, q, ctx.tok_pos, ctx.tok_entry, cache.block_table,
+                              cache.storage if self.own_kv else None, cache.page_size)
         att = ctx.ws.rows("qna_att", T, self.nh * hd, self.dtype)
         self.core.run(q, att, ctx, cache)
         if self.gate or hd != self.dv:
