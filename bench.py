@@ -175,7 +175,7 @@ def timeline_step(args) -> int:
     raw = dict(CONFIG_05B if args.sizes == "0.5b" else CONFIG_8B)
     raw["num_hidden_layers"] = args.layers or 4
     if args.design != "default":                  # one of the pair of `--workload designs`, at the first of --design-sizes
-        pair = {"gopitar": gopitar_pair, "somipel": somipel_pair}.get(args.design, design_pair)
+        pair = {"gopitar": gopitar_pair, "somipel": somipel_pair, "zokuzen": zokuzen_pair}.get(args.design, design_pair)
         raw = pair(args.design_sizes.split(",")[0], args.layers or 4)[1 if args.design == "dense" else 0]
         raw["num_hidden_layers"] = args.layers or 4
     cfg = config_from_json(raw)
@@ -333,6 +333,36 @@ def somipel_pair(size: str, layers: int):
     return sp, gopitar_pair(size, layers)[0]
 
 
+def zokuzen_pair(size: str, layers: int):
+    """(Zokuzen configuration, Nirozen configuration of the same width, depth, heads, head size, latent width, vocabulary, experts
+    and expert sizes: the framework's other design with latent attention and routed experts.) Of every four layers the first
+    mixes by attention over runs of 1,024 positions (2 kv heads, half of each head rotated), the second by latent attention over
+    a window of 1,024, the third by the channel-decay recurrence, the fourth by attention over the first's keys and values; four
+    copies of the residual stream; two identity units beside the experts."""
+    nz = design_pair(size, layers)[0]
+    W, V = nz["width"], nz["vocab"]
+    m0, f0 = nz["layers"][0]["mixer"], nz["layers"][0]["mlp"]
+    H, d, r = m0["heads"], m0["dim"], m0["kv_rank"]
+    mlp = {"kind": "moe", "expert": {"ff": f0["expert"]["ff"]}, "shared": {"ff": f0["shared"]["ff"]},
+           "router": {"experts": f0["router"]["experts"], "top": f0["router"]["top"], "identity": 2, "scale": 2.0}}
+
+    def att(kv_from=None):
+        m = {"heads": H, "kv_heads": 2, "dim": d, "vdim": d, "scale": d ** -0.5, "mask": {"size": 1024}, "rot": {"dims": d // 2, "base": 1e6}}
+        if kv_from is not None:
+            m["kv_from"] = kv_from
+        return {"type": "attention", "mixer": m, "mlp": dict(mlp)}
+
+    def layer(i):
+        if i % 4 == 1:
+            return {"type": "latent_attention", "mixer": {"heads": H, "dim": d, "vdim": d, "kv_rank": r, "scale": d ** -0.5, "mask": {"size": 1024}},
+                    "mlp": dict(mlp)}
+        if i % 4 == 2:
+            return {"type": "wkv", "mixer": {"heads": W // 64, "dim": 64}, "mlp": dict(mlp)}
+        return att(i - 3 if i % 4 == 3 else None)
+    zk = {"architecture": "Zokuzen", "vocab": V, "width": W, "streams": 4, "norm": {"eps": 1e-5}, "layers": [layer(i) for i in range(layers)]}
+    return zk, nz
+
+
 class OpTimer:
     """Brackets every kernel wrapper of `infinilm_b200.ops`, every library product of `Linear` and the library's grouped
     product with CUDA events on the launching stream, for steps that run eagerly; `table()` gives microseconds and calls per name."""
@@ -352,7 +382,7 @@ class OpTimer:
             e1.record()
             lab = label or name
             if lab == "matrix_state_scan":
-                lab += {1: " delta", 3: " gated"}.get(a[0], " decay") + (" single" if k.get("single") else "") + (" segmented" if k.get("seg_len") else "")
+                lab += {1: " delta", 3: " gated", 4: " channel decay"}.get(a[0], " decay") + (" single" if k.get("single") else "") + (" segmented" if k.get("seg_len") else "")
             elif lab == "short_conv":
                 lab += f"[{a[10]}x{a[11]}]"
             if lab == "linear":
@@ -375,7 +405,8 @@ class OpTimer:
                      "attention_prefill", "attention_prefill_tc5", "gemm_skinny", "gemm_skinny_resid", "gemm_skinny_rope", "gemm_mid",
                      "gemm_tc5", "latent_norm_store", "moe_route", "moe_sort", "moe_combine", "gather_rows", "gemm_grouped", "short_conv",
                      "short_conv_state", "delta_prep", "matrix_state_scan", "group_norm_gate", "head_gate", "scaled_sum", "softcap", "silu_cols", "norm_add", "cast_rows",
-                     "qk_norm_store", "gate_pack", "stabilized_gates"):
+                     "qk_norm_store", "gate_pack", "stabilized_gates", "hyper_step", "qk_rows_norm_rope_store", "token_shift_mix",
+                     "double_exp_decay", "tanh_rows", "moe_select", "moe_route_sort_small"):
             self._wrap(ops, name)
         self._wrap(Linear, "__call__", "linear")
         if hasattr(F, "grouped_mm"):
@@ -414,8 +445,8 @@ def run_designs(args) -> int:
         rec = {"workload": "designs", "size": size, "layers": L, "dtype": "bf16", "data": "synthetic", "peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": src}}
         family = getattr(args, "design_family", "nirozen")
         rec["design"] = family
-        pair = {"gopitar": gopitar_pair, "somipel": somipel_pair}.get(family, design_pair)
-        for which, raw in zip((family, "gopitar" if family == "somipel" else "dense_gqa"), pair(size, L)):
+        pair = {"gopitar": gopitar_pair, "somipel": somipel_pair, "zokuzen": zokuzen_pair}.get(family, design_pair)
+        for which, raw in zip((family, {"somipel": "gopitar", "zokuzen": "nirozen"}.get(family, "dense_gqa")), pair(size, L)):
             cfg = config_from_json(raw)
             B = 64
             eng = Engine.from_tensors(cfg, random_tensors(cfg, 0, "cuda:0"), dtype="bfloat16", page_size=PAGE,
@@ -516,10 +547,11 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--no-graph", action="store_true", help="do not replay decode steps as CUDA graphs")
     ap.add_argument("--points", type=str, default="1,64", help="batch sizes of the extra decode points")
-    ap.add_argument("--design", choices=["default", "nirozen", "gopitar", "somipel", "dense"], default="default",
+    ap.add_argument("--design", choices=["default", "nirozen", "gopitar", "somipel", "zokuzen", "dense"], default="default",
                     help="--timeline: the step of one of the pair of --workload designs instead of the benchmark model")
-    ap.add_argument("--design-family", choices=["nirozen", "gopitar", "somipel"], default="nirozen",
-                    help="--workload designs: which design stands beside the dense GQA model of equal size (somipel: beside gopitar)")
+    ap.add_argument("--design-family", choices=["nirozen", "gopitar", "somipel", "zokuzen"], default="nirozen",
+                    help="--workload designs: which design stands beside the dense GQA model of equal size (somipel: beside gopitar; "
+                         "zokuzen: beside nirozen)")
     ap.add_argument("--design-sizes", type=str, default="1k,2k", help="--workload designs: layer sizes to run (1k, 2k, 4k)")
     ap.add_argument("--workload", choices=["default", "long_context", "continuous", "designs"], default="default",
                     help="default: the benchmark line. long_context: 8 requests x 16,384-token prompts at 8B sizes, prompt "

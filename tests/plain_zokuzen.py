@@ -146,22 +146,27 @@ def wkv_mixer(h, p, m, eps, state=None):
 
 
 # ---- the routed feed-forward --------------------------------------------------------------------------------------------
-def route(h, w_router, correction, top, scale):
+def route(h, w_router, correction, top, scale, margins=None):
     """Scores are the softmax of the router's logits over all its outputs; the `top` largest of score + correction are
     chosen (the lower index wins a tie); the weights are the chosen scores themselves over their sum (+ 1e-20), times scale.
-    Returns (idx [T, top], weights [T, top])."""
+    Returns (idx [T, top], weights [T, top]). margins (a list, or None) receives per token the gap between the last chosen and
+    the first rejected choice score (infinite where every output is chosen): how far rounding is from turning the choice."""
     s = torch.softmax(h @ w_router.T, dim=-1)
     c = s + correction
-    order = torch.sort(c, dim=-1, descending=True, stable=True).indices[:, :top]
+    full = torch.sort(c, dim=-1, descending=True, stable=True)
+    order = full.indices[:, :top]
+    if margins is not None:
+        v = full.values
+        margins.append(v[:, top - 1] - v[:, top] if top < v.shape[1] else torch.full((h.shape[0],), math.inf, dtype=h.dtype))
     chosen = torch.gather(s, 1, order)
     return order, chosen / (chosen.sum(-1, keepdim=True) + 1e-20) * scale
 
 
-def routed_feed_forward(h, p, f):
+def routed_feed_forward(h, p, f, margins=None):
     """f: the layer's "mlp" object. The last router.identity outputs of the router stand for units that return their input."""
     r = f["router"]
     n, n_id, top = r["experts"], r.get("identity", 0), r["top"]
-    idx, wt = route(h, p["router"], p["correction"], top, r.get("scale", 1.0))
+    idx, wt = route(h, p["router"], p["correction"], top, r.get("scale", 1.0), margins)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for j in range(top):
@@ -179,9 +184,9 @@ def sub(tensors, prefix):
     return {k[len(prefix) + 1:]: v for k, v in tensors.items() if k.startswith(prefix + ".")}
 
 
-def forward(cfg, tensors, tokens, dtype=torch.float64, want_layers=False):
+def forward(cfg, tensors, tokens, dtype=torch.float64, want_layers=False, margins=None):
     """cfg: the parsed config.json; tensors: name -> tensor. Returns logits [T, vocab] (and the sum of the residual streams
-    after every layer, [layers, T, W])."""
+    after every layer, [layers, T, W]). margins: a list that receives every router's choice margins (see `route`)."""
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in tensors.items()}
     eps, S = cfg["norm"]["eps"], int(cfg.get("streams", 1))
     x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)]
@@ -203,7 +208,7 @@ def forward(cfg, tensors, tokens, dtype=torch.float64, want_layers=False):
         xs = streams_write(xs, y, hc1["mix"], hc1["out"])
         if L.get("mlp") is not None:
             h = rms_norm(streams_read(xs, hc2["in"]), w[f"l{i}.norm2"], eps, one_plus=True)
-            xs = streams_write(xs, routed_feed_forward(h, sub(w, f"l{i}.mlp"), L["mlp"]), hc2["mix"], hc2["out"])
+            xs = streams_write(xs, routed_feed_forward(h, sub(w, f"l{i}.mlp"), L["mlp"], margins), hc2["mix"], hc2["out"])
         sums.append(xs.sum(0))
     logits = rms_norm(xs.sum(0), w["final.norm"], eps, one_plus=True) @ w["embed"].T
     return (logits, torch.stack(sums)) if want_layers else logits

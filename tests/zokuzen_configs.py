@@ -105,7 +105,7 @@ def make_weights(raw: dict, seed: int, peak: float = 4.0) -> Dict[str, torch.Ten
         elif typ == "wkv" and name.endswith((".mix.r", ".mix.k", ".mix.v", ".mix.g")):
             x = x * 4.0
         elif name.endswith(".mix.w0"):
-            x = x * 1.5 - 3.0                     # decays mostly near one (exp(-exp(-3)) = 0.95): the state carries far
+            x = x * 1.5 - 6.5                     # decays mostly near one (exp(-exp(-6.5)) = 0.9985): the state carries hundreds of tokens
         elif name.endswith(".mix.w1"):
             x = x * 10.0
         elif name.endswith(".mix.u"):
@@ -113,9 +113,9 @@ def make_weights(raw: dict, seed: int, peak: float = 4.0) -> Dict[str, torch.Ten
         elif ".mix.mu." in name:
             x = torch.rand(x.shape, generator=g)
         elif name.endswith(".correction"):
-            x = x * 10.0                          # of the scores' own size (about 1 / outputs): it changes choices
+            x = x * 5.0                           # of the scores' own size (about 1 / outputs): it changes choices
         elif name.endswith(".router"):
-            x = x * 1.0
+            x = x * 0.3                           # logits of size one: scores that move with the token but do not saturate
         elif name.endswith(".shared.sg"):
             x = x * 3.0
         elif name.endswith(".mix") and ".hc" in name:
