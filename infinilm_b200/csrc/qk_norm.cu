@@ -218,6 +218,7 @@ IL_EXPORT int il_gate_pack(const void* y, int act_kind, int hd, const void* gate
 // pass. Queries go to q_out [T, nh * hd], keys to the K plane of the token's cache slot, values to the V plane, heads laid
 // out at hd columns with the surplus zero. k_off < 0: no keys or values (the mixer reads another layer's cache).
 // Sums of squares, angles and the rotation are f32. One block per token.
+#define QR_MAX_ROT 1024
 template <typename TA>
 __global__ void qk_rows_norm_rope_store_kernel(const TA* proj, int ld, int q_off, int k_off, int v_off, int nh, int nkv, int dk, int dv, int hd,
                                                const void* __restrict__ wq, const void* __restrict__ wk, int w_kind, float eps, int rot,
@@ -225,11 +226,13 @@ __global__ void qk_rows_norm_rope_store_kernel(const TA* proj, int ld, int q_off
                                                const int* __restrict__ tok_pos, const int* __restrict__ tok_entry,
                                                const int* __restrict__ block_table, int bt_stride, TA* __restrict__ cache, int page_size) {
     __shared__ float red[32];
+    __shared__ float s_cos[QR_MAX_ROT / 2], s_sin[QR_MAX_ROT / 2];      // the token's angles, once for all its heads
     const int t = blockIdx.x;
     const int pos = tok_pos[t];
     const bool has_k = k_off >= 0;
     int page = -1;
     if (has_k && cache) page = block_table[(size_t)tok_entry[t] * bt_stride + pos / page_size];
+    for (int i = threadIdx.x; i < (rot >> 1); i += blockDim.x) sincosf((float)pos * inv_freq[i], &s_sin[i], &s_cos[i]);
     il_pdl_wait();
     const TA* row = proj + (size_t)t * ld;
     const int nq = nh * dk, nk = nkv * dk, half = rot >> 1;
@@ -254,8 +257,7 @@ __global__ void qk_rows_norm_rope_store_kernel(const TA* proj, int ld, int q_off
         const bool low = d < half;
         const int c2 = low ? c + half : c - half;
         const float b = il_to_f(x[c2]) * r * il_load_any(w, w_kind, c2);
-        float s, co;
-        sincosf((float)pos * inv_freq[low ? d : d - half], &s, &co);
+        const float s = s_sin[low ? d : d - half], co = s_cos[low ? d : d - half];
         return low ? a * co - b * s : a * co + b * s;
     };
     for (int idx = threadIdx.x; idx < nh * hd; idx += blockDim.x) {
@@ -280,6 +282,7 @@ IL_EXPORT int il_qk_rows_norm_rope_store(const void* proj, int act_kind, int ld,
     if (T <= 0) return IL_OK;
     if (nh <= 0 || nkv <= 0 || dk <= 0 || dv <= 0 || hd < dk || hd < dv || page_size <= 0 || !wq || (k_off >= 0 && !wk)) return IL_BAD_ARG;
     if (rot < 0 || (rot & 1) || rot > dk || (rot > 0 && !inv_freq)) return IL_BAD_ARG;
+    if (rot > QR_MAX_ROT) return IL_UNSUPPORTED;
     const int work = nh * hd;
     const int threads = work >= 2048 ? 512 : work >= 512 ? 256 : 128;
     if (act_kind == IL_F32)

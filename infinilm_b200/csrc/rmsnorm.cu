@@ -251,8 +251,9 @@ IL_EXPORT int il_cast_rows(const float* x, void* out, int out_kind, long long to
 //   sum_out (or null): sum_out[r] = sum_t x_t              (the stream as one row: what the model's last norm reads)
 // Everything is f32 but y (read) and normed (written), which have the compute dtype. S <= HC_MAX_STREAMS.
 // Dynamic shared memory: H floats (u between its two passes).
-#define HC_MAX_STREAMS 8
-template <typename TA>
+#define HC_MAX_STREAMS 16
+// (MAXS: the copies a thread holds in registers, 4, 8 or 16 - the smallest that takes S)
+template <typename TA, int MAXS>
 __global__ void hyper_step_kernel(float* streams, const float* init, const TA* y, const float* __restrict__ mix,
                                   const float* __restrict__ out_w, const float* __restrict__ in_next, const void* __restrict__ w, int w_kind,
                                   float eps, TA* __restrict__ normed, float* __restrict__ sum_out, int S, int H) {
@@ -260,7 +261,7 @@ __global__ void hyper_step_kernel(float* streams, const float* init, const TA* y
     __shared__ float red[32];
     __shared__ float s_mix[HC_MAX_STREAMS * HC_MAX_STREAMS], s_out[HC_MAX_STREAMS], s_in[HC_MAX_STREAMS];
     const int r = blockIdx.x;
-    if (threadIdx.x < S * S && y) s_mix[threadIdx.x] = mix[threadIdx.x];
+    for (int i = threadIdx.x; i < S * S && y; i += blockDim.x) s_mix[i] = mix[i];
     if (threadIdx.x < S) {
         if (y) s_out[threadIdx.x] = out_w[threadIdx.x];
         if (in_next) s_in[threadIdx.x] = in_next[threadIdx.x];
@@ -270,42 +271,42 @@ __global__ void hyper_step_kernel(float* streams, const float* init, const TA* y
     float* xr = streams + (size_t)r * S * H;
     float ss = 0.f;
     for (int h = threadIdx.x; h < H; h += blockDim.x) {
-        float x[HC_MAX_STREAMS], xn[HC_MAX_STREAMS];
+        float x[MAXS], xn[MAXS];
 #pragma unroll
-        for (int s = 0; s < HC_MAX_STREAMS; ++s)
+        for (int s = 0; s < MAXS; ++s)
             if (s < S) x[s] = init ? init[(size_t)r * H + h] : xr[(size_t)s * H + h];
         if (y) {
             const float yv = il_to_f(y[(size_t)r * H + h]);
 #pragma unroll
-            for (int t = 0; t < HC_MAX_STREAMS; ++t)
+            for (int t = 0; t < MAXS; ++t)
                 if (t < S) {
                     float a = 0.f;
 #pragma unroll
-                    for (int s = 0; s < HC_MAX_STREAMS; ++s)
+                    for (int s = 0; s < MAXS; ++s)
                         if (s < S) a = fmaf(s_mix[s * S + t], x[s], a);
                     xn[t] = fmaf(s_out[t], yv, a);
                 }
         } else {
 #pragma unroll
-            for (int t = 0; t < HC_MAX_STREAMS; ++t)
+            for (int t = 0; t < MAXS; ++t)
                 if (t < S) xn[t] = x[t];
         }
         if (y || init) {
 #pragma unroll
-            for (int t = 0; t < HC_MAX_STREAMS; ++t)
+            for (int t = 0; t < MAXS; ++t)
                 if (t < S) xr[(size_t)t * H + h] = xn[t];
         }
         if (sum_out) {
             float a = 0.f;
 #pragma unroll
-            for (int t = 0; t < HC_MAX_STREAMS; ++t)
+            for (int t = 0; t < MAXS; ++t)
                 if (t < S) a += xn[t];
             sum_out[(size_t)r * H + h] = a;
         }
         if (in_next) {
             float u = 0.f;
 #pragma unroll
-            for (int t = 0; t < HC_MAX_STREAMS; ++t)
+            for (int t = 0; t < MAXS; ++t)
                 if (t < S) u = fmaf(s_in[t], xn[t], u);
             us[h] = u;
             ss += u * u;
@@ -318,6 +319,93 @@ __global__ void hyper_step_kernel(float* streams, const float* init, const TA* y
         normed[(size_t)r * H + h] = il_from_f<TA>(us[h] * rstd * il_load_any(w, w_kind, h));
 }
 
+// The same with four neighbouring columns a thread (H a multiple of 4, rows on 16-byte borders): 16-byte loads of the copies,
+// all of a thread's loads issued before the first use. Every column's sums run in the scalar kernel's order.
+template <typename TA, int MAXS>
+__global__ void __launch_bounds__(256) hyper_step_vec_kernel(float* streams, const float* init, const TA* y, const float* __restrict__ mix,
+                                                             const float* __restrict__ out_w, const float* __restrict__ in_next,
+                                                             const void* __restrict__ w, int w_kind, float eps, TA* __restrict__ normed,
+                                                             float* __restrict__ sum_out, int S, int H) {
+    extern __shared__ __align__(16) float us[];
+    __shared__ float red[32];
+    __shared__ float s_mix[MAXS * MAXS], s_out[MAXS], s_in[MAXS];
+    const int r = blockIdx.x;
+    for (int i = threadIdx.x; i < S * S && y; i += blockDim.x) s_mix[i] = mix[i];
+    if (threadIdx.x < S) {
+        if (y) s_out[threadIdx.x] = out_w[threadIdx.x];
+        if (in_next) s_in[threadIdx.x] = in_next[threadIdx.x];
+    }
+    il_pdl_wait();
+    __syncthreads();
+    float* xr = streams + (size_t)r * S * H;
+    const int nv = H >> 2;
+    float ss = 0.f;
+    for (int v = threadIdx.x; v < nv; v += blockDim.x) {
+        const int h = 4 * v;
+        float4 x[MAXS], xn[MAXS];
+        if (init) {
+            const float4 e = ld4(init + (size_t)r * H + h);
+#pragma unroll
+            for (int s = 0; s < MAXS; ++s) x[s] = e;
+        } else {
+#pragma unroll
+            for (int s = 0; s < MAXS; ++s)
+                if (s < S) x[s] = ld4(xr + (size_t)s * H + h);
+        }
+        if (y) {
+            const float4 yv = ld4(y + (size_t)r * H + h);
+#pragma unroll
+            for (int t = 0; t < MAXS; ++t)
+                if (t < S) {
+                    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int s = 0; s < MAXS; ++s)
+                        if (s < S) {
+                            const float m = s_mix[s * S + t];
+                            a.x = fmaf(m, x[s].x, a.x), a.y = fmaf(m, x[s].y, a.y), a.z = fmaf(m, x[s].z, a.z), a.w = fmaf(m, x[s].w, a.w);
+                        }
+                    const float o = s_out[t];
+                    xn[t] = make_float4(fmaf(o, yv.x, a.x), fmaf(o, yv.y, a.y), fmaf(o, yv.z, a.z), fmaf(o, yv.w, a.w));
+                }
+        } else {
+#pragma unroll
+            for (int t = 0; t < MAXS; ++t) xn[t] = x[t];
+        }
+        if (y || init) {
+#pragma unroll
+            for (int t = 0; t < MAXS; ++t)
+                if (t < S) st4(xr + (size_t)t * H + h, xn[t]);
+        }
+        if (sum_out) {
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int t = 0; t < MAXS; ++t)
+                if (t < S) a.x += xn[t].x, a.y += xn[t].y, a.z += xn[t].z, a.w += xn[t].w;
+            st4(sum_out + (size_t)r * H + h, a);
+        }
+        if (in_next) {
+            float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int t = 0; t < MAXS; ++t)
+                if (t < S) {
+                    const float m = s_in[t];
+                    u.x = fmaf(m, xn[t].x, u.x), u.y = fmaf(m, xn[t].y, u.y), u.z = fmaf(m, xn[t].z, u.z), u.w = fmaf(m, xn[t].w, u.w);
+                }
+            *reinterpret_cast<float4*>(us + h) = u;
+            ss += (u.x * u.x + u.y * u.y) + (u.z * u.z + u.w * u.w);
+        }
+    }
+    if (!in_next) return;
+    ss = il_block_sum(ss, red);
+    const float rstd = 1.f / sqrtf(ss / (float)H + eps);
+    for (int v = threadIdx.x; v < nv; v += blockDim.x) {
+        const int h = 4 * v;
+        const float4 u = *reinterpret_cast<const float4*>(us + h);
+        const float4 wv = w_kind == IL_F32 ? ld4((const float*)w + h) : ld4((const __nv_bfloat16*)w + h);
+        st4(normed + (size_t)r * H + h, make_float4(u.x * rstd * wv.x, u.y * rstd * wv.y, u.z * rstd * wv.z, u.w * rstd * wv.w));
+    }
+}
+
 IL_EXPORT int il_hyper_step(float* streams, const float* init, const void* y, int act_kind, const float* mix, const float* out_w,
                             const float* in_next, const void* w, int w_kind, float eps, void* normed, float* sum_out, int S, int H, int T,
                             cudaStream_t stream) {
@@ -326,16 +414,37 @@ IL_EXPORT int il_hyper_step(float* streams, const float* init, const void* y, in
     const size_t smem = (size_t)H * sizeof(float);
     if (smem > 200 * 1024) return IL_UNSUPPORTED;
     const int threads = H >= 4096 ? 512 : H >= 1024 ? 256 : 128;
-    if (act_kind == IL_F32) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(hyper_step_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        IL_LAUNCH(hyper_step_kernel<float>, T, threads, smem, stream, streams, init, (const float*)y, mix, out_w, in_next, w, w_kind, eps,
-                  (float*)normed, sum_out, S, H);
-    } else if (act_kind == IL_BF16) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(hyper_step_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        IL_LAUNCH(hyper_step_kernel<__nv_bfloat16>, T, threads, smem, stream, streams, init, (const __nv_bfloat16*)y, mix, out_w, in_next, w, w_kind,
-                  eps, (__nv_bfloat16*)normed, sum_out, S, H);
-    } else
-        return IL_BAD_ARG;
+    // four columns a thread where rows are whole 16-byte pieces (and the copies fit the registers)
+    const bool vec = (H & 3) == 0 && S <= 8 &&
+                     (((uintptr_t)streams | (uintptr_t)init | (uintptr_t)y | (uintptr_t)w | (uintptr_t)normed | (uintptr_t)sum_out) & 15) == 0;
+    const int vthreads = H >= 1024 ? 256 : H >= 512 ? 128 : 64;
+#define HC_GO(TA, MAXS)                                                                                                                  \
+    do {                                                                                                                                 \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(hyper_step_kernel<TA, MAXS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        IL_LAUNCH((hyper_step_kernel<TA, MAXS>), T, threads, smem, stream, streams, init, (const TA*)y, mix, out_w, in_next, w, w_kind, eps, \
+                  (TA*)normed, sum_out, S, H);                                                                                           \
+    } while (0)
+#define HC_GOV(TA, MAXS)                                                                                                                     \
+    do {                                                                                                                                     \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(hyper_step_vec_kernel<TA, MAXS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        IL_LAUNCH((hyper_step_vec_kernel<TA, MAXS>), T, vthreads, smem, stream, streams, init, (const TA*)y, mix, out_w, in_next, w, w_kind, \
+                  eps, (TA*)normed, sum_out, S, H);                                                                                          \
+    } while (0)
+#define HC_PICK(TA)                                          \
+    do {                                                     \
+        if (vec && S <= 2) HC_GOV(TA, 2);                    \
+        else if (vec && S <= 4) HC_GOV(TA, 4);               \
+        else if (vec) HC_GOV(TA, 8);                         \
+        else if (S <= 4) HC_GO(TA, 4);                       \
+        else if (S <= 8) HC_GO(TA, 8);                       \
+        else HC_GO(TA, 16);                                  \
+    } while (0)
+    if (act_kind == IL_F32) HC_PICK(float);
+    else if (act_kind == IL_BF16) HC_PICK(__nv_bfloat16);
+    else return IL_BAD_ARG;
+#undef HC_PICK
+#undef HC_GOV
+#undef HC_GO
     IL_LAUNCH_CHECK();
     return IL_OK;
 }

@@ -700,7 +700,7 @@ IL_EXPORT int il_matrix_state_scan(int mode, const float* q, const float* k, con
         // (measured at 16 heads of 128 x 128 over 2,048 tokens: 945 -> 695 us); the delta rule, whose sum over the lanes
         // stands between a token's two updates, loses by the longer shuffle chain (648 -> 771 us) and keeps 16.
         int dpt = dim <= 32 ? 8 : 16;
-        if (mode == 0 && dim > 32 && dim <= 128) {
+        if ((mode == 0 || mode == 4) && dim > 32 && dim <= 128) {       // (the channel decay, like the decayed sum, has no sum over the lanes between a token's updates)
             const int cols16 = SR_THREADS / ((dim + 15) / 16 <= 1 ? 1 : (dim <= 32 ? 2 : dim <= 64 ? 4 : 8));
             if ((long long)(seg_len > 0 ? n_tiles : E) * H * ((vdim + cols16 - 1) / cols16) <= 148) dpt = 8;     // at most one block an SM otherwise
         }
@@ -1000,20 +1000,72 @@ __global__ void token_shift_mix_kernel(const TA* __restrict__ h, int ldh, const 
     }
 }
 
+// Four neighbouring columns a thread (W a multiple of 4, rows on 16-byte borders): 8- or 16-byte loads and stores.
+__device__ __forceinline__ float4 ts_ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 ts_ld4(const __nv_bfloat16* p) {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x), b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+__device__ __forceinline__ void ts_st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void ts_st4(__nv_bfloat16* p, float4 v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<const uint32_t*>(&a);
+    u.y = *reinterpret_cast<const uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+template <typename TA>
+__global__ void token_shift_mix4_kernel(const TA* __restrict__ h, int ldh, const float* __restrict__ mu, int n_mix, float* state,
+                                        size_t slot_stride, const int* __restrict__ read_slots, const int* __restrict__ write_slots,
+                                        const int* __restrict__ tok_entry, const int* __restrict__ qstart, TA* __restrict__ out, int ldo,
+                                        int W, int T) {
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (c >= W) return;
+    for (int t = blockIdx.y; t < T; t += gridDim.y) {
+        const int e = tok_entry[t];
+        const int first = qstart[e];
+        const float4 cur = ts_ld4(h + (size_t)t * ldh + c);
+        float4 prev;
+        if (t == first) {
+            prev = ts_ld4(state + (size_t)read_slots[e] * slot_stride + c);
+            if (write_slots) ts_st4(state + (size_t)write_slots[e] * slot_stride + c, ts_ld4(h + (size_t)(qstart[e + 1] - 1) * ldh + c));
+        } else {
+            prev = ts_ld4(h + (size_t)(t - 1) * ldh + c);
+        }
+        const float4 d = make_float4(prev.x - cur.x, prev.y - cur.y, prev.z - cur.z, prev.w - cur.w);
+        for (int m = 0; m < n_mix; ++m) {
+            const float4 u = ts_ld4(mu + (size_t)m * W + c);
+            ts_st4(out + (size_t)t * ldo + (size_t)m * W + c, make_float4(fmaf(d.x, u.x, cur.x), fmaf(d.y, u.y, cur.y), fmaf(d.z, u.z, cur.z), fmaf(d.w, u.w, cur.w)));
+        }
+    }
+}
+
 IL_EXPORT int il_token_shift_mix(const void* h, int kind, int ldh, const float* mu, int n_mix, float* state, long long slot_stride,
                                  const int* read_slots, const int* write_slots, const int* tok_entry, const int* qstart, void* out, int ldo,
                                  int W, int T, cudaStream_t stream) {
     if (T <= 0) return IL_OK;
     if (W <= 0 || n_mix <= 0 || ldo < n_mix * W || slot_stride < W) return IL_BAD_ARG;
+    if (kind != IL_F32 && kind != IL_BF16) return IL_BAD_ARG;
+    if (((W | ldh | ldo | (int)(slot_stride & 3)) & 3) == 0 && (((uintptr_t)h | (uintptr_t)mu | (uintptr_t)state | (uintptr_t)out) & 15) == 0) {
+        const int threads = W >= 512 ? 128 : 64;
+        const dim3 grid4((W / 4 + threads - 1) / threads, T < 32768 ? T : 32768);
+        if (kind == IL_F32)
+            token_shift_mix4_kernel<float><<<grid4, threads, 0, stream>>>((const float*)h, ldh, mu, n_mix, state, (size_t)slot_stride, read_slots,
+                                                                          write_slots, tok_entry, qstart, (float*)out, ldo, W, T);
+        else
+            token_shift_mix4_kernel<__nv_bfloat16><<<grid4, threads, 0, stream>>>((const __nv_bfloat16*)h, ldh, mu, n_mix, state, (size_t)slot_stride,
+                                                                                  read_slots, write_slots, tok_entry, qstart, (__nv_bfloat16*)out, ldo, W, T);
+        IL_LAUNCH_CHECK();
+        return IL_OK;
+    }
     const dim3 grid((W + 127) / 128, T < 32768 ? T : 32768);
     if (kind == IL_F32)
         token_shift_mix_kernel<float><<<grid, 128, 0, stream>>>((const float*)h, ldh, mu, n_mix, state, (size_t)slot_stride, read_slots, write_slots,
                                                                 tok_entry, qstart, (float*)out, ldo, W, T);
-    else if (kind == IL_BF16)
+    else
         token_shift_mix_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)h, ldh, mu, n_mix, state, (size_t)slot_stride, read_slots,
                                                                         write_slots, tok_entry, qstart, (__nv_bfloat16*)out, ldo, W, T);
-    else
-        return IL_BAD_ARG;
     IL_LAUNCH_CHECK();
     return IL_OK;
 }

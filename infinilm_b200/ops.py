@@ -255,7 +255,7 @@ def norm_add(resid: torch.Tensor, branch: torch.Tensor, weight: torch.Tensor, ep
              _stream()), "norm_add")
 
 
-HYPER_MAX_STREAMS = 8
+HYPER_MAX_STREAMS = 16
 
 
 def hyper_step(streams: torch.Tensor, n_streams: int, *, init: Optional[torch.Tensor] = None, y: Optional[torch.Tensor] = None,

@@ -76,7 +76,7 @@ class RoutedExperts(FeedForward):
     def weight_specs(self) -> List[WeightSpec]:
         specs = [WeightSpec("router", (self.n_out, self.hidden), init=("normal", 0.3))]
         if self.router_bias:
-            specs.append(WeightSpec(self.bias_name, (self.n_out,), "vector", ("normal", 0.3 if self.rule == ops.ROUTE_TOP_LOGITS else 0.02)))
+            specs.append(WeightSpec(self.bias_name, (self.n_out,), "vector", ("normal", 0.3 if self.rule == ops.ROUTE_TOP_LOGITS else 0.002)))
         if self.has_sg:
             specs.append(WeightSpec("shared.sg", (1, self.hidden), init=("normal", 0.1)))
         for e in range(self.n):
@@ -91,6 +91,9 @@ class RoutedExperts(FeedForward):
 
     def set_weights(self, t: Dict[str, torch.Tensor]) -> None:
         rows = [t["router"]] + ([t["shared.sg"]] if self.has_sg else [])       # the gate's row behind the router's
+        if self.extended and (self.n_out + len(rows) - 1) % 8:                  # zero rows up to a multiple of 8: the library's product of
+            pad = -(self.n_out + len(rows) - 1) % 8                             # many rows is far slower on an odd number of outputs
+            rows.append(torch.zeros((pad, self.hidden), dtype=t["router"].dtype, device=t["router"].device))
         self.router = torch.cat(rows, dim=0).to(self.dtype).contiguous()
         self.router_lin = None
         if self.extended or (self.dtype == torch.bfloat16 and self.hidden % 8 == 0 and not bool(self.params.get("own_products_only", False))):

@@ -30,7 +30,7 @@ def _close(got, ref, dtype, what, tol=None):
 
 # ---- several copies of the residual stream -----------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("T,S,H", [(1, 1, 72), (5, 2, 120), (33, 3, 256), (4, 4, 2048), (2, 8, 13), (3, 5, 5000)])
+@pytest.mark.parametrize("T,S,H", [(1, 1, 72), (5, 2, 120), (33, 3, 256), (4, 4, 2048), (2, 8, 13), (3, 5, 5000), (2, 16, 40)])
 def test_step_between_sublayers(cuda_device, dtype, T, S, H):
     from infinilm_b200 import ops
     g = torch.Generator().manual_seed(T * S + H)
@@ -394,7 +394,7 @@ class _Ctx:
         self.ws, self.dtype, self.tap = Workspace(torch.device("cuda"), max_tokens), dtype, None
 
 
-def _moe_part(raw_mlp, W, dtype, seed, scale_corr=10.0):
+def _moe_part(raw_mlp, W, dtype, seed, scale_corr=100.0):
     from infinilm_b200.parts.moe import RoutedExperts
     r = raw_mlp["router"]
     part = RoutedExperts({"hidden": W, "n_experts": r["experts"], "top": r["top"], "expert_ff": raw_mlp["expert"]["ff"],

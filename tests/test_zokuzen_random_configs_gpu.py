@@ -27,7 +27,7 @@ def _random_moe(rng):
 
 def random_config(seed: int) -> dict:
     rng = random.Random(7000 + seed)
-    width = rng.choice([40, 72, 96, 136, 200, 256])
+    width = rng.choice([40, 72, 96, 100, 136, 200, 256])
     layers, owners = [], []
     for i in range(rng.randint(1, 5)):
         mlp, r = _random_moe(rng), rng.random()

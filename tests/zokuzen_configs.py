@@ -113,7 +113,7 @@ def make_weights(raw: dict, seed: int, peak: float = 4.0) -> Dict[str, torch.Ten
         elif ".mix.mu." in name:
             x = torch.rand(x.shape, generator=g)
         elif name.endswith(".correction"):
-            x = x * 5.0                           # of the scores' own size (about 1 / outputs): it changes choices
+            x = x * 50.0                          # of the scores' own size (about 1 / outputs): it changes choices
         elif name.endswith(".router"):
             x = x * 0.3                           # logits of size one: scores that move with the token but do not saturate
         elif name.endswith(".shared.sg"):
