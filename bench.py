@@ -344,10 +344,10 @@ def zokuzen_pair(size: str, layers: int):
     m0, f0 = nz["layers"][0]["mixer"], nz["layers"][0]["mlp"]
     H, d, r = m0["heads"], m0["dim"], m0["kv_rank"]
     mlp = {"kind": "moe", "expert": {"ff": f0["expert"]["ff"]}, "shared": {"ff": f0["shared"]["ff"]},
-           "router": {"experts": f0["router"]["experts"], "top": f0["router"]["top"], "identity": 2, "scale": 2.0}}
+           "router": {"experts": f0["router"]["experts"], "top": f0["router"]["top"], "identity": 2, "scale": 2.5}}
 
     def att(kv_from=None):
-        m = {"heads": H, "kv_heads": 2, "dim": d, "vdim": d, "scale": d ** -0.5, "mask": {"size": 1024}, "rot": {"dims": d // 2, "base": 1e6}}
+        m = {"heads": H, "kv_heads": 2, "dim": d, "vdim": d, "scale": d ** -0.5, "mask": {"size": 1024}, "rot": {"dims": d // 2, "base": 5e5}}
         if kv_from is not None:
             m["kv_from"] = kv_from
         return {"type": "attention", "mixer": m, "mlp": dict(mlp)}

@@ -188,11 +188,11 @@ def _run_attention(kernel, c, nh, nkv, hd, scale, mask_arg, dtype, splits=1):
     return out
 
 
-MASKS = [("chunk", 24), ("chunk", 16), ("chunk", 200), ("chunk", 5), ("chunk", 1), ("window", 20), ("window", 96), ("window", 1), ("window", 17)]
+MASKS = [("chunk", 24), ("chunk", 16), ("chunk", 210), ("chunk", 5), ("chunk", 1), ("window", 20), ("window", 90), ("window", 1), ("window", 17)]
 
 
 @pytest.mark.parametrize("kernel,dtype,nh,nkv,hd", [("plain", "float32", 3, 1, 40), ("plain", "bfloat16", 6, 3, 48), ("prefill", "bfloat16", 6, 3, 48),
-                                                    ("prefill", "bfloat16", 8, 8, 96), ("tc5", "bfloat16", 4, 2, 64), ("tc5", "bfloat16", 9, 1, 128),
+                                                    ("prefill", "bfloat16", 8, 8, 80), ("tc5", "bfloat16", 4, 2, 64), ("tc5", "bfloat16", 9, 1, 128),
                                                     ("tc5", "bfloat16", 4, 1, 256)])
 def test_masks_over_portions(cuda_device, kernel, dtype, nh, nkv, hd):
     """Portions that start and end anywhere against runs of positions and windows of several sizes, with one key made to stand
@@ -200,8 +200,8 @@ def test_masks_over_portions(cuda_device, kernel, dtype, nh, nkv, hd):
     that may see the key follows it; one that may not must not."""
     starts, qlens = [0, 250, 31, 16, 0], [70, 9, 2, 33, 1]
     for kind, size in MASKS:
-        marks = [None, (1, 255), (1, 240), (0, 0), (0, 23), (0, 24), (0, 47), (0, 48), (3, 15), (3, 16), (3, 31), (1, 258 - size if size < 200 else 199),
-                 (1, 259 - size if size < 200 else 200)]
+        marks = [None, (1, 255), (1, 240), (0, 0), (0, 23), (0, 24), (0, 47), (0, 48), (3, 15), (3, 16), (3, 31), (1, 258 - size if size < 200 else 209),
+                 (1, 259 - size if size < 200 else 210)]
         for mk in marks[:5] + marks[5 + (size % 4) * 2: 7 + (size % 4) * 2] + marks[-2:]:
             c = _attn_case(nh, nkv, hd, starts, qlens, nh * hd + size, mk)
             got = _run_attention(kernel, c, nh, nkv, hd, 0.2, -size if kind == "chunk" else size, dtype)
@@ -209,11 +209,11 @@ def test_masks_over_portions(cuda_device, kernel, dtype, nh, nkv, hd):
 
 
 @pytest.mark.parametrize("kernel,dtype,nh,nkv,hd,splits", [("plain", "float32", 3, 1, 40, 1), ("decode", "bfloat16", 6, 3, 48, 1), ("decode", "bfloat16", 3, 1, 64, 4),
-                                                           ("decode", "bfloat16", 8, 1, 96, 3), ("decode", "bfloat16", 4, 2, 128, 7), ("decode", "bfloat16", 2, 2, 256, 2)])
+                                                           ("decode", "bfloat16", 8, 1, 80, 3), ("decode", "bfloat16", 4, 2, 128, 7), ("decode", "bfloat16", 2, 2, 256, 2)])
 def test_masks_of_single_tokens(cuda_device, kernel, dtype, nh, nkv, hd, splits):
     """Single tokens at lengths around page borders and around every mask's edges: the token at a run's first position sees
     itself alone; the one before it sees its whole run; a window's oldest key is seen, the one before it is not."""
-    starts, qlens = [0, 15, 16, 17, 399, 63, 23, 24, 47, 48, 200, 199], [1] * 12
+    starts, qlens = [0, 15, 16, 17, 399, 63, 23, 24, 47, 48, 210, 209], [1] * 12
     for kind, size in MASKS:
         for mk in (None, (4, 399), (4, 400 - size if kind == "window" else (399 // size) * size), (4, max(0, 399 - size) if kind == "window" else max(0, (399 // size) * size - 1)),
                    (5, 48), (5, 47)):
@@ -413,8 +413,8 @@ def _moe_part(raw_mlp, W, dtype, seed, scale_corr=100.0):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("W,ff,experts,top,identity,scale,shared", [(96, 40, 4, 2, 1, 1.5, 48), (120, 56, 3, 6, 3, 2.0, 64), (128, 32, 8, 3, 2, 2.0, None),
-                                                                      (72, 24, 2, 1, 0, 1.0, 40), (256, 96, 8, 3, 2, 2.0, 128), (100, 20, 1, 2, 1, 0.5, 12)])
+@pytest.mark.parametrize("W,ff,experts,top,identity,scale,shared", [(96, 40, 4, 2, 1, 1.5, 48), (120, 56, 3, 6, 3, 2.0, 64), (128, 32, 7, 4, 2, 2.0, None),
+                                                                      (72, 24, 2, 1, 0, 1.0, 40), (256, 88, 9, 3, 2, 1.5, 136), (100, 20, 1, 2, 1, 0.5, 12)])
 def test_routed_feed_forward_with_identity_units_and_gated_shared_unit(cuda_device, dtype, W, ff, experts, top, identity, scale, shared):
     mlp = {"expert": {"ff": ff}, "router": {"experts": experts, "top": top, "identity": identity, "scale": scale}}
     if shared:

@@ -34,10 +34,10 @@ def random_config(seed: int) -> dict:
         if r < 0.3:
             layers.append(_wkv(rng.randint(1, 5), rng.choice([4, 8, 12, 20, 32, 64, 128]), mlp))
         elif r < 0.55:
-            layers.append(_lat(rng.randint(1, 6), rng.choice([4, 8, 16, 24, 64]), rng.choice([4, 12, 32, 80]), rng.choice([8, 16, 24, 48, 96, 128, 272]),
-                               round(rng.uniform(0.05, 0.4), 3), rng.choice([1, 2, 15, 16, 17, 40, 96, 1000]), mlp))
+            layers.append(_lat(rng.randint(1, 6), rng.choice([4, 8, 16, 24, 64]), rng.choice([4, 12, 32, 80]), rng.choice([8, 16, 24, 48, 80, 128, 272]),
+                               round(rng.uniform(0.05, 0.4), 3), rng.choice([1, 2, 15, 16, 17, 40, 90, 1000]), mlp))
         else:
-            chunk = rng.choice([1, 3, 16, 17, 32, 50, 200, 1000])
+            chunk = rng.choice([1, 3, 16, 17, 32, 50, 210, 1000])
             if owners and rng.random() < 0.45:
                 src = rng.choice(owners)
                 m = layers[src]["mixer"]

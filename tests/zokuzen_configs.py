@@ -58,7 +58,7 @@ def zk_c() -> dict:
     # four streams; head size 128 (the tensor-memory prefill kernel) without rotation; a chunk longer than most test
     # sequences and one of 5; a window of 1 (a token sees itself alone); a latent of 128 under 2 heads of 128
     return {"architecture": "Zokuzen", "vocab": 128, "width": 128, "streams": 4, "norm": {"eps": 1e-6},
-            "layers": [_att(2, 1, 128, 128, 0.09, 400, None, _moe(32, 8, 3, 2, 2.0, 32)),
+            "layers": [_att(2, 1, 128, 128, 0.09, 400, None, _moe(32, 7, 3, 2, 2.5, 32)),
                        _att(2, 1, 128, 128, 0.12, 5, None, None, kv_from=0),
                        _lat(2, 128, 128, 128, 0.06, 1, _moe(32, 2, 1, 0, 1.0, 16)),
                        _wkv(8, 16, _moe(16, 2, 2, 1, 3.0, None)),
