@@ -54,7 +54,8 @@ class Linear:
             return out
         if self.use_tc5 and ops.tc5_ok(x.shape[0], self.in_features) and (out_f32 or out.dtype == torch.bfloat16):
             if self._tc5_scratch is None:
-                need = max(ops.gemm_tc5_scratch_bytes(m, self.out_features, self.in_features) for m in (32, 64, 128, 256))
+                # (the number of K slices falls as the rows grow, so the bytes are not monotone in the rows: every row count is asked)
+                need = max(ops.gemm_tc5_scratch_bytes(m, self.out_features, self.in_features) for m in range(ops.SKINNY_MAX_ROWS + 1, ops.TC5_MAX_ROWS + 1))
                 self._tc5_scratch = torch.empty(max(need // 4, 1), dtype=torch.float32, device=x.device)
             ops.gemm_tc5(x, self.weight, out, self.alpha, self.bias, self._tc5_scratch)
             return out

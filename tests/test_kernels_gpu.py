@@ -578,6 +578,25 @@ def test_gemm_tc5(cuda_device, M, N, K, out_dtype):
     close(out, (x.double() @ w.double().t()).float(), "float32" if out_dtype == "float32" else "bfloat16")
 
 
+@pytest.mark.parametrize("N,K", [(4099, 192), (2000, 512), (32000, 1024), (333, 136)])
+def test_output_head_at_every_row_count(cuda_device, N, K):
+    """A `Linear` that may take its own tcgen05 products (the output head) keeps one scratch buffer for all of them: it has to
+    hold the K slices of every row count from 17 to 256 - their number falls as the rows grow, so the bytes needed are not
+    largest at the largest count."""
+    from infinilm_b200.parts.linear import Linear
+    g = torch.Generator(device="cuda").manual_seed(N)
+    lin = Linear(K, N, torch.bfloat16, use_tc5=True)
+    w = (torch.randn(N, K, device="cuda", generator=g) / math.sqrt(K)).bfloat16()
+    lin.set(w)
+    for M in list(range(17, 257, 13)) + [64, 65, 100, 128, 129, 255, 256]:
+        x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+        out = torch.full((M, N), float("nan"), device="cuda")
+        lin(x, out, out_f32=True)
+        close(out, (x.double() @ w.double().t()).float(), "float32")
+    torch.cuda.synchronize()
+    assert int(ops.stream_status("cuda:0").item()) == 0
+
+
 @pytest.mark.parametrize("M,N,K", [(17, 97, 64), (32, 128, 72), (64, 331, 200), (128, 513, 1000), (64, 4608, 4096), (33, 300, 264),
                                    (40, 4096, 16384)])
 @pytest.mark.parametrize("out_dtype", ["bfloat16", "float32"])
