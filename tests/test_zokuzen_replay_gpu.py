@@ -39,7 +39,8 @@ _oracle_cache = {}
 
 
 def _weights(name, seed, dtype):
-    return make_weights(ZOKUZEN[name](), seed, peak=PEAK[dtype])
+    # (bfloat16: routing choices that rounding cannot turn, so that every position is compared)
+    return make_weights(ZOKUZEN[name](), seed, peak=PEAK[dtype], clear_choices=dtype == "bfloat16")
 
 
 def _plain(raw, w, ids):
@@ -66,7 +67,7 @@ def _check(got, oracle, dtype, what, cum=True):
     got, ref = got.double().cpu(), ref.double()
     assert got.shape == ref.shape and torch.isfinite(got).all(), what
     keep = (torch.cummin(margin, 0).values if cum else margin) > MARGIN[dtype]
-    assert dtype == "bfloat16" or keep.float().mean() > 0.5, f"{what}: the test's weights leave too few clear choices"
+    assert keep.float().mean() > (0.5 if dtype == "float32" else 0.99), f"{what}: the test's weights leave too few clear choices"
     got, ref = got - got.mean(dim=-1, keepdim=True), ref - ref.mean(dim=-1, keepdim=True)
     err = (got - ref).pow(2).mean(dim=-1).sqrt() / ref.pow(2).mean(dim=-1).sqrt()
     err = torch.where(keep, err, torch.zeros_like(err))
@@ -202,7 +203,7 @@ def test_a_marked_token_at_the_masks_edges_and_at_page_borders(cuda_device, name
     (24 and 17 in "a", 9 in "d"), of the windows (20; 7) and around page borders from the token whose logits are compared,
     in a prompt, in portions and decoded alone: a key that is seen one position too long, or lost one too early, moves them."""
     raw = ZOKUZEN[name]()
-    w = make_weights(raw, seed, peak=PEAK[dtype])
+    w = make_weights(raw, seed, peak=PEAK[dtype], clear_choices=dtype == "bfloat16")
     w["embed"][5] = (w["embed"][5].float() * 4.0).to(torch.bfloat16)        # the marked token
     eng = _engine(raw, w, dtype)
     base = [t if t != 5 else 6 for t in token_ids(64, raw["vocab"], 12)]
@@ -223,7 +224,7 @@ def test_a_far_token_reaches_the_end(cuda_device, dtype):
     one): every attention layer of this configuration has forgotten it - and the engine must follow the plain implementation
     there, whole, decoded and in portions."""
     raw = ZOKUZEN["a"]()
-    w = make_weights(raw, 13, peak=PEAK[dtype])
+    w = make_weights(raw, 13, peak=PEAK[dtype], clear_choices=dtype == "bfloat16")
     ids = token_ids(300, raw["vocab"], 14)
     other = [(ids[0] + 1) % raw["vocab"]] + ids[1:]
     ref, ref2 = _plain(raw, w, ids), _plain(raw, w, other)
@@ -240,7 +241,7 @@ def test_greedy_generation_through_llm(cuda_device, dtype):
     from infinilm_b200.config import config_from_json
     from infinilm_b200.llm import LLM, SamplingParams
     raw = ZOKUZEN["c"]()
-    w = make_weights(raw, 4, peak=PEAK[dtype])
+    w = make_weights(raw, 4, peak=PEAK[dtype], clear_choices=dtype == "bfloat16")
     prompts = [token_ids(n, raw["vocab"], 30 + n) for n in (5, 21, 40)]
     with warnings.catch_warnings():
         warnings.simplefilter("ignore", RuntimeWarning)
@@ -279,7 +280,7 @@ def test_trace_runner_as_a_process(cuda_device, tmp_path):
     """A model folder (the head is the embedding table: no tensor of its own) replayed step by step by the runner."""
     from infinilm_b200.weights.safetensors_io import write_safetensors
     raw = ZOKUZEN["b"]()
-    w = make_weights(raw, 6, peak=PEAK["bfloat16"])
+    w = make_weights(raw, 6, peak=PEAK["bfloat16"], clear_choices=True)
     folder = str(tmp_path / "m")
     os.makedirs(folder)
     with open(os.path.join(folder, "config.json"), "w") as f:

@@ -78,10 +78,13 @@ def zk_d() -> dict:
 ZOKUZEN = {"a": zk_a, "b": zk_b, "c": zk_c, "d": zk_d}
 
 
-def make_weights(raw: dict, seed: int, peak: float = 4.0) -> Dict[str, torch.Tensor]:
+def make_weights(raw: dict, seed: int, peak: float = 4.0, clear_choices: bool = False) -> Dict[str, torch.Tensor]:
     """`peak`: the standard deviation the scaled scores of an attention layer are brought to (through the query norm's weight
     where queries are normed, through the query projection otherwise): a few keys then carry most of the weight, while
-    rounding to bfloat16 does not yet decide which."""
+    rounding to bfloat16 does not yet decide which.
+    `clear_choices`: the routers' corrections are spread evenly over -0.4 .. 0.4 (in a drawn order) and their logits made
+    small, so that no choice lies within rounding of turning: every position of a bfloat16 run can then be compared (the
+    weights still follow the token through the scores)."""
     from infinilm_b200.config import config_from_json
     from infinilm_b200.weights import random_tensors
     w = random_tensors(config_from_json(raw), seed, "cpu")
@@ -114,8 +117,10 @@ def make_weights(raw: dict, seed: int, peak: float = 4.0) -> Dict[str, torch.Ten
             x = torch.rand(x.shape, generator=g)
         elif name.endswith(".correction"):
             x = x * 50.0                          # of the scores' own size (about 1 / outputs): it changes choices
+            if clear_choices:
+                x = torch.linspace(-0.4, 0.4, x.numel())[torch.randperm(x.numel(), generator=g)]
         elif name.endswith(".router"):
-            x = x * 0.3                           # logits of size one: scores that move with the token but do not saturate
+            x = x * (0.015 if clear_choices else 0.3)     # logits of size one: scores that move with the token but do not saturate
         elif name.endswith(".shared.sg"):
             x = x * 3.0
         elif name.endswith(".mix") and ".hc" in name:
